@@ -14,7 +14,7 @@ tail -c 3000 "$OUT/bench_n1.json"; tail -n 5 "$OUT/bench_n1.err"
 timeout 600 python tools/bench_kernels.py --only attn > "$OUT/attn_micro.jsonl" 2> "$OUT/attn_micro.err"; echo "attn micro rc=$?" | tee -a "$OUT/summary.txt"
 cat "$OUT/attn_micro.jsonl"
 timeout 300 python tools/profile_target.py attn > "$OUT/plain_attn.log" 2>&1 && \
-timeout 900 ncu --set full --clock-control none --import-source on -k regex:fa_.*_tc_kernel -c 4 -f -o "$OUT/attn_prof" \
+timeout 900 ncu --set full --clock-control none -k regex:fa_.*_tc_kernel -c 4 -f -o "$OUT/attn_prof" \
     python tools/profile_target.py attn > "$OUT/ncu_attn.log" 2>&1; echo "ncu rc=$?" | tee -a "$OUT/summary.txt"
 tail -n 5 "$OUT/ncu_attn.log"
 cat "$OUT/summary.txt"

@@ -1,0 +1,397 @@
+// Sparse mixture-of-experts feed-forward without host synchronisation: router, expert GEMVs that follow the expert
+// index on the device ("selective loading": only the chosen experts' weights are touched), clamped gated activation,
+// and the weighted combination in fp32.  bf16 or fp32 activations / expert weights; router in fp32.
+//
+//   router        z = Wr h;  s = softmax(z);  choice = s + correction;  the `top` largest choices are taken,
+//                 weight = s * out_scale (not renormalised);  optional second output sigmoid(<w_sg, h>) per token
+//   activation    g = min(gate, limit), u = clamp(up, -limit, limit);  a = g * sigmoid(alpha * g) * (u + 1)
+//   expert index >= E means an identity expert: its output is the token's input itself
+// Expert weights are stored [E, in, out] (the layout of the grouped expert layers), gate | up fused on the out dim.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float ldf(const float* p) { return *p; }
+__device__ __forceinline__ float ldf(const bf16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void stf(float* p, float v) { *p = v; }
+__device__ __forceinline__ void stf(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+__device__ __forceinline__ void ld2(const float* p, float& a, float& b) {
+    const float2 v = *reinterpret_cast<const float2*>(p);
+    a = v.x;
+    b = v.y;
+}
+__device__ __forceinline__ void ld2(const bf16* p, float& a, float& b) {
+    const float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(p));
+    a = v.x;
+    b = v.y;
+}
+
+__device__ __forceinline__ float glu_act(float g, float u, float limit, float alpha) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + expf(-alpha * g)) * (u + 1.f);
+}
+
+// ---- router ---------------------------------------------------------------------------------------------------------
+constexpr int RT_WARPS = 4, RT_GROUP = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(RT_WARPS * 32)
+moe_router_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ corr,
+                  const float* __restrict__ wsg, int* __restrict__ idx, float* __restrict__ wts,
+                  float* __restrict__ sgate, long long N, int W, int R, int top, float out_scale) {
+    extern __shared__ float smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* ps = smem + (long long)warp * 2 * R;     // probabilities
+    float* cs = ps + R;                             // choice scores
+    const long long n = (long long)blockIdx.x * RT_WARPS + warp;
+    if (n >= N) return;
+    const T* hr = h + n * W;
+    for (int r0 = 0; r0 < R; r0 += RT_GROUP) {
+        float acc[RT_GROUP];
+#pragma unroll
+        for (int i = 0; i < RT_GROUP; ++i) acc[i] = 0.f;
+        for (int c = lane; c < W; c += 32) {
+            const float hv = ldf(hr + c);
+#pragma unroll
+            for (int i = 0; i < RT_GROUP; ++i)
+                if (r0 + i < R) acc[i] = fmaf(hv, wr[(long long)(r0 + i) * W + c], acc[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < RT_GROUP; ++i) {
+            const float z = warp_sum(acc[i]);
+            if (lane == 0 && r0 + i < R) ps[r0 + i] = z;
+        }
+    }
+    if (wsg != nullptr && sgate != nullptr) {
+        float a = 0.f;
+        for (int c = lane; c < W; c += 32) a = fmaf(ldf(hr + c), wsg[c], a);
+        a = warp_sum(a);
+        if (lane == 0) sgate[n] = 1.f / (1.f + expf(-a));
+    }
+    __syncwarp();
+    float mx = -INFINITY;
+    for (int r = lane; r < R; r += 32) mx = fmaxf(mx, ps[r]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int r = lane; r < R; r += 32) sum += expf(ps[r] - mx);
+    sum = warp_sum(sum);
+    const float inv = 1.f / sum;
+    __syncwarp();
+    for (int r = lane; r < R; r += 32) {
+        const float p = expf(ps[r] - mx) * inv;
+        ps[r] = p;
+        cs[r] = p + (corr != nullptr ? corr[r] : 0.f);
+    }
+    __syncwarp();
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int r = lane; r < R; r += 32) {
+            const float c = cs[r];
+            if (c > best) {       // lanes scan upwards: the lowest index wins a tie inside a lane
+                best = c;
+                bi = r;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) {
+                best = ob;
+                bi = oi;
+            }
+        }
+        if (bi >= R) bi = 0;      // every score NaN: keep the index in range
+        if (lane == 0) {
+            idx[n * top + k] = bi;
+            wts[n * top + k] = ps[bi] * out_scale;
+            cs[bi] = -INFINITY;
+        }
+        __syncwarp();
+    }
+}
+
+// ---- gate/up GEMV + activation for (token, expert) pairs ----------------------------------------------------------------
+constexpr int GV_WARPS = 8;
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(GV_WARPS * 32)
+moe_gate_up_act_kernel(const T* __restrict__ h, const T* __restrict__ wgu, const int* __restrict__ idx,
+                       T* __restrict__ act, int pairs_per_token, int W, int F, int E, float limit, float alpha) {
+    extern __shared__ float smem[];
+    constexpr int PER = VEC ? 2 : 1, COLS = 32 * PER;
+    float* hs = smem;                                  // [W]
+    float* red = smem + W;                             // [GV_WARPS][COLS][2]
+    const long long p = blockIdx.x;
+    const int e = idx != nullptr ? idx[p] : 0;
+    if (e < 0 || e >= E) return;                       // identity expert: no intermediate
+    const long long t = p / pairs_per_token;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int c = threadIdx.x; c < W; c += GV_WARPS * 32) hs[c] = ldf(h + t * W + c);
+    __syncthreads();
+    const int f0 = blockIdx.y * COLS + lane * PER;
+    const int per = (W + GV_WARPS - 1) / GV_WARPS;
+    const int k_lo = warp * per, k_hi = min(W, k_lo + per);
+    float g0 = 0.f, g1 = 0.f, u0 = 0.f, u1 = 0.f;
+    if (f0 < F) {
+        const T* base = wgu + (long long)e * W * 2 * F;
+#pragma unroll 4
+        for (int k = k_lo; k < k_hi; ++k) {
+            const T* row = base + (long long)k * 2 * F;
+            const float hv = hs[k];
+            if (VEC) {
+                float a, b, c, d;
+                ld2(row + f0, a, b);
+                ld2(row + F + f0, c, d);
+                g0 = fmaf(hv, a, g0);
+                g1 = fmaf(hv, b, g1);
+                u0 = fmaf(hv, c, u0);
+                u1 = fmaf(hv, d, u1);
+            } else {
+                g0 = fmaf(hv, ldf(row + f0), g0);
+                u0 = fmaf(hv, ldf(row + F + f0), u0);
+            }
+        }
+    }
+    float* mine = red + ((long long)warp * COLS + lane * PER) * 2;
+    mine[0] = g0;
+    mine[1] = u0;
+    if (VEC) {
+        mine[2] = g1;
+        mine[3] = u1;
+    }
+    __syncthreads();
+    if (threadIdx.x < COLS) {
+        const int f = blockIdx.y * COLS + threadIdx.x;
+        if (f < F) {
+            float g = 0.f, u = 0.f;
+#pragma unroll
+            for (int w = 0; w < GV_WARPS; ++w) {
+                g += red[((long long)w * COLS + threadIdx.x) * 2];
+                u += red[((long long)w * COLS + threadIdx.x) * 2 + 1];
+            }
+            stf(act + p * F + f, glu_act(g, u, limit, alpha));
+        }
+    }
+}
+
+// ---- down GEMV + weighted combination (+ identity experts, + gated shared expert) -> fp32 ---------------------------
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(GV_WARPS * 32)
+moe_down_combine_kernel(const T* __restrict__ act, const T* __restrict__ wd, const int* __restrict__ idx,
+                        const float* __restrict__ wts, const T* __restrict__ h, const T* __restrict__ act_s,
+                        const T* __restrict__ wds, const float* __restrict__ sgate, float* __restrict__ y, int top, int W,
+                        int F, int Fs, int E) {
+    constexpr int PER = VEC ? 2 : 1, COLS = 32 * PER;
+    __shared__ float red[GV_WARPS][COLS];
+    const long long t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int c0 = blockIdx.y * COLS + lane * PER;
+    float a0 = 0.f, a1 = 0.f;
+    if (c0 < W) {
+        for (int j = 0; j < top; ++j) {
+            const int e = idx[t * top + j];
+            const float wgt = wts[t * top + j];
+            if (e < 0 || e >= E) {
+                if (warp == 0) {
+                    a0 = fmaf(wgt, ldf(h + t * W + c0), a0);
+                    if (VEC) a1 = fmaf(wgt, ldf(h + t * W + c0 + 1), a1);
+                }
+                continue;
+            }
+            const T* arow = act + (t * top + j) * F;
+            const T* base = wd + (long long)e * F * W;
+            const int per = (F + GV_WARPS - 1) / GV_WARPS;
+            const int f_lo = warp * per, f_hi = min(F, f_lo + per);
+            float s0 = 0.f, s1 = 0.f;
+#pragma unroll 4
+            for (int f = f_lo; f < f_hi; ++f) {
+                const float av = ldf(arow + f);
+                if (VEC) {
+                    float p, q;
+                    ld2(base + (long long)f * W + c0, p, q);
+                    s0 = fmaf(av, p, s0);
+                    s1 = fmaf(av, q, s1);
+                } else {
+                    s0 = fmaf(av, ldf(base + (long long)f * W + c0), s0);
+                }
+            }
+            a0 = fmaf(wgt, s0, a0);
+            a1 = fmaf(wgt, s1, a1);
+        }
+        if (act_s != nullptr) {
+            const float wgt = sgate != nullptr ? sgate[t] : 1.f;
+            const T* arow = act_s + t * Fs;
+            const int per = (Fs + GV_WARPS - 1) / GV_WARPS;
+            const int f_lo = warp * per, f_hi = min(Fs, f_lo + per);
+            float s0 = 0.f, s1 = 0.f;
+#pragma unroll 4
+            for (int f = f_lo; f < f_hi; ++f) {
+                const float av = ldf(arow + f);
+                if (VEC) {
+                    float p, q;
+                    ld2(wds + (long long)f * W + c0, p, q);
+                    s0 = fmaf(av, p, s0);
+                    s1 = fmaf(av, q, s1);
+                } else {
+                    s0 = fmaf(av, ldf(wds + (long long)f * W + c0), s0);
+                }
+            }
+            a0 = fmaf(wgt, s0, a0);
+            a1 = fmaf(wgt, s1, a1);
+        }
+    }
+    red[warp][lane * PER] = a0;
+    if (VEC) red[warp][lane * PER + 1] = a1;
+    __syncthreads();
+    if (threadIdx.x < COLS) {
+        const int c = blockIdx.y * COLS + threadIdx.x;
+        if (c < W) {
+            float s = 0.f;
+#pragma unroll
+            for (int w = 0; w < GV_WARPS; ++w) s += red[w][threadIdx.x];
+            y[t * W + c] = s;
+        }
+    }
+}
+
+// ---- pieces of the sorted (GEMM) path: activation over [M, 2F], gather-combine -------------------------------------------
+template <typename T>
+__global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out, long long M, int F, float limit,
+                                   float alpha) {
+    const long long total = M * F;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long m = i / F;
+        const int f = (int)(i - m * F);
+        stf(out + i, glu_act(ldf(gu + m * 2 * F + f), ldf(gu + m * 2 * F + F + f), limit, alpha));
+    }
+}
+
+template <typename T>
+__global__ void moe_gather_combine_kernel(const T* __restrict__ ys, const int* __restrict__ slot,
+                                          const int* __restrict__ idx, const float* __restrict__ wts,
+                                          const T* __restrict__ h, const T* __restrict__ shared_out,
+                                          const float* __restrict__ sgate, float* __restrict__ y, int top, int W, int E) {
+    const long long t = blockIdx.x;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float a = 0.f;
+        for (int j = 0; j < top; ++j) {
+            const int e = idx[t * top + j];
+            const float wgt = wts[t * top + j];
+            const float v = (e < 0 || e >= E) ? ldf(h + t * W + c) : ldf(ys + (long long)slot[t * top + j] * W + c);
+            a = fmaf(wgt, v, a);
+        }
+        if (shared_out != nullptr) a = fmaf(sgate != nullptr ? sgate[t] : 1.f, ldf(shared_out + t * W + c), a);
+        y[t * W + c] = a;
+    }
+}
+
+}  // namespace
+
+// dtype: 0 bf16, 1 fp32 (activations and expert weights).  R = router outputs (experts + identity experts).
+NXD_API int nxd_moe_router(int dtype, const void* h, const float* wr, const float* corr, const float* wsg, int* idx,
+                           float* wts, float* sgate, long long N, int W, int R, int top, float out_scale, void* stream) {
+    if (N == 0) return 0;
+    NXD_REQUIRE(top >= 1 && top <= R, "router: top %d of %d", top, R);
+    const size_t smem = (size_t)RT_WARPS * 2 * R * sizeof(float);
+    NXD_REQUIRE(smem <= 48 * 1024, "router: %d outputs", R);
+    const unsigned blocks = (unsigned)((N + RT_WARPS - 1) / RT_WARPS);
+    if (dtype == 0)
+        moe_router_kernel<bf16><<<blocks, RT_WARPS * 32, smem, (cudaStream_t)stream>>>((const bf16*)h, wr, corr, wsg, idx,
+                                                                                      wts, sgate, N, W, R, top, out_scale);
+    else
+        moe_router_kernel<float><<<blocks, RT_WARPS * 32, smem, (cudaStream_t)stream>>>((const float*)h, wr, corr, wsg,
+                                                                                       idx, wts, sgate, N, W, R, top,
+                                                                                       out_scale);
+    NXD_LAUNCH_CHECK();
+    return 0;
+}
+
+// act[p, :] = activation(h[p / pairs_per_token] @ wgu[idx[p]]) for P pairs; idx NULL = expert 0 for every pair (a dense
+// gated MLP); pairs whose index is outside [0, E) are identity experts and are skipped.
+NXD_API int nxd_moe_gate_up_act(int dtype, const void* h, const void* wgu, const int* idx, void* act, long long P,
+                                int pairs_per_token, int W, int F, int E, float limit, float alpha, void* stream) {
+    if (P == 0) return 0;
+    NXD_REQUIRE(P < (1ll << 31), "gate/up: %lld pairs", P);
+    const bool vec = (F % 2) == 0;
+    const int cols = vec ? 64 : 32;
+    const size_t smem = (size_t)(W + GV_WARPS * cols * 2) * sizeof(float);
+    NXD_REQUIRE(smem <= 200 * 1024, "gate/up: input width %d", W);
+    dim3 grid((unsigned)P, (F + cols - 1) / cols);
+    cudaStream_t st = (cudaStream_t)stream;
+#define NXD_GU(T, V)                                                                                                  \
+    do {                                                                                                              \
+        auto kern = moe_gate_up_act_kernel<T, V>;                                                                     \
+        if (smem > 48 * 1024)                                                                                         \
+            NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));       \
+        kern<<<grid, GV_WARPS * 32, smem, st>>>((const T*)h, (const T*)wgu, idx, (T*)act, pairs_per_token, W, F, E,   \
+                                                limit, alpha);                                                        \
+    } while (0)
+    if (dtype == 0) {
+        if (vec) NXD_GU(bf16, true); else NXD_GU(bf16, false);
+    } else {
+        if (vec) NXD_GU(float, true); else NXD_GU(float, false);
+    }
+#undef NXD_GU
+    NXD_LAUNCH_CHECK();
+    return 0;
+}
+
+// y[t] = sum_j wts[t, j] * (idx[t, j] in [0, E) ? act[t * top + j] @ wd[idx[t, j]] : h[t])
+//        + (act_s ? (sgate ? sgate[t] : 1) * act_s[t] @ wds : 0)                                  -> fp32 [N, W]
+NXD_API int nxd_moe_down_combine(int dtype, const void* act, const void* wd, const int* idx, const float* wts,
+                                 const void* h, const void* act_s, const void* wds, const float* sgate, float* y,
+                                 long long N, int top, int W, int F, int Fs, int E, void* stream) {
+    if (N == 0) return 0;
+    NXD_REQUIRE(N < (1ll << 31), "down/combine: %lld tokens", N);
+    const bool vec = (W % 2) == 0;
+    const int cols = vec ? 64 : 32;
+    dim3 grid((unsigned)N, (W + cols - 1) / cols);
+    cudaStream_t st = (cudaStream_t)stream;
+#define NXD_DC(T, V)                                                                                                  \
+    moe_down_combine_kernel<T, V><<<grid, GV_WARPS * 32, 0, st>>>((const T*)act, (const T*)wd, idx, wts, (const T*)h, \
+                                                                  (const T*)act_s, (const T*)wds, sgate, y, top, W, F,  \
+                                                                  Fs, E)
+    if (dtype == 0) {
+        if (vec) NXD_DC(bf16, true); else NXD_DC(bf16, false);
+    } else {
+        if (vec) NXD_DC(float, true); else NXD_DC(float, false);
+    }
+#undef NXD_DC
+    NXD_LAUNCH_CHECK();
+    return 0;
+}
+
+NXD_API int nxd_clamped_glu(int dtype, const void* gate_up, void* out, long long M, int F, float limit, float alpha,
+                            void* stream) {
+    if (M == 0) return 0;
+    long long blocks = (M * F + 255) / 256;
+    const long long cap = (long long)nxd_num_sms() * 16;
+    if (blocks > cap) blocks = cap;
+    if (dtype == 0)
+        clamped_glu_kernel<bf16><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const bf16*)gate_up, (bf16*)out, M, F,
+                                                                                    limit, alpha);
+    else
+        clamped_glu_kernel<float><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const float*)gate_up, (float*)out, M,
+                                                                                     F, limit, alpha);
+    NXD_LAUNCH_CHECK();
+    return 0;
+}
+
+// ys [pairs, W]: expert outputs in sorted order, slot [N, top]: row of ys of every (token, choice); identity experts read h.
+NXD_API int nxd_moe_gather_combine(int dtype, const void* ys, const int* slot, const int* idx, const float* wts,
+                                   const void* h, const void* shared_out, const float* sgate, float* y, long long N,
+                                   int top, int W, int E, void* stream) {
+    if (N == 0) return 0;
+    NXD_REQUIRE(N < (1ll << 31), "combine: %lld tokens", N);
+    if (dtype == 0)
+        moe_gather_combine_kernel<bf16><<<(unsigned)N, 128, 0, (cudaStream_t)stream>>>(
+            (const bf16*)ys, slot, idx, wts, (const bf16*)h, (const bf16*)shared_out, sgate, y, top, W, E);
+    else
+        moe_gather_combine_kernel<float><<<(unsigned)N, 128, 0, (cudaStream_t)stream>>>(
+            (const float*)ys, slot, idx, wts, (const float*)h, (const float*)shared_out, sgate, y, top, W, E);
+    NXD_LAUNCH_CHECK();
+    return 0;
+}

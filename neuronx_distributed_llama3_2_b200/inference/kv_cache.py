@@ -10,10 +10,14 @@ Paged mode has two flavours: the static identity mapping (every line owns ``max_
 (``runtime.native.PagedKVPool``): lines get pages as they grow (``reserve``), give them back (``free``), can be forked
 copy-on-write (``fork``) and rolled back (``truncate``).  The block table is a device tensor updated in place, so CUDA
 graphs that captured it see the new mapping.
+
+Layers need not be alike: ``layer_specs[i] = (kv_heads, key_dim, value_dim)`` gives layer ``i`` its own shapes (key and
+value sizes may differ), and ``share_from[i] = j`` makes layer ``i`` read layer ``j``'s keys and values instead of
+holding its own (cross-layer KV sharing: ``layer(i)`` returns ``j``'s tensors, nothing is allocated for ``i``).
 """
 from __future__ import annotations
 
-from typing import Iterable, List, Optional, Tuple
+from typing import Dict, Iterable, List, Optional, Tuple
 
 import torch
 
@@ -21,8 +25,14 @@ import torch
 class KVCache:
     def __init__(self, num_layers: int, lines: int, kv_heads: int, seq_len: int, head_dim: int,
                  dtype: torch.dtype = torch.bfloat16, device=None, paged: bool = False, page_size: int = 128,
-                 num_pages: Optional[int] = None):
+                 num_pages: Optional[int] = None, layer_specs: Optional[List[Optional[Tuple[int, int, int]]]] = None,
+                 share_from: Optional[Dict[int, int]] = None):
         self.num_layers, self.lines, self.kv_heads, self.seq_len, self.head_dim = num_layers, lines, kv_heads, seq_len, head_dim
+        self.share_from = dict(share_from or {})
+        for i, j in self.share_from.items():
+            if j in self.share_from or not (0 <= j < num_layers) or j == i:
+                raise ValueError(f"layer {i} cannot share the keys/values of layer {j}")
+        specs = layer_specs if layer_specs is not None else [(kv_heads, head_dim, head_dim)] * num_layers
         self.paged, self.page_size = paged, page_size
         self.pool = None
         if paged:
@@ -37,18 +47,34 @@ class KVCache:
                 n_pages = num_pages
                 self.pool = PagedKVPool(n_pages, page_size, lines, self.max_pages)
                 self.block_table = torch.zeros(lines, self.max_pages, dtype=torch.int32, device=device)
-            shape = (n_pages, kv_heads, page_size, head_dim)
+            lead, rows = n_pages, page_size
         else:
-            shape = (lines, kv_heads, seq_len, head_dim)
+            lead, rows = lines, seq_len
             self.block_table = None
-        self.k: List[torch.Tensor] = [torch.zeros(shape, dtype=dtype, device=device) for _ in range(num_layers)]
-        self.v: List[torch.Tensor] = [torch.zeros(shape, dtype=dtype, device=device) for _ in range(num_layers)]
+        self.k: List[Optional[torch.Tensor]] = []
+        self.v: List[Optional[torch.Tensor]] = []
+        for i in range(num_layers):
+            if i in self.share_from:
+                self.k.append(None)
+                self.v.append(None)
+                continue
+            g, dk, dv = specs[i]
+            self.k.append(torch.zeros((lead, g, rows, dk), dtype=dtype, device=device))
+            self.v.append(torch.zeros((lead, g, rows, dv), dtype=dtype, device=device))
+
+    def owns(self, i: int) -> bool:
+        """False for a layer that reads another layer's keys and values."""
+        return i not in self.share_from
 
     def layer(self, i: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        i = self.share_from.get(i, i)
         return self.k[i], self.v[i]
 
+    def _tensors(self) -> List[torch.Tensor]:
+        return [t for t in self.k + self.v if t is not None]
+
     def reset(self) -> None:
-        for t in self.k + self.v:
+        for t in self._tensors():
             t.zero_()
         if self.pool is not None:
             for line in range(self.lines):
@@ -81,7 +107,7 @@ class KVCache:
             self.sync_lines([line])
 
     def _copy_page(self, src: int, dst: int) -> None:
-        for t in self.k + self.v:
+        for t in self._tensors():
             t[dst].copy_(t[src])
 
     def fork(self, src: int, dst: int) -> None:
@@ -102,4 +128,4 @@ class KVCache:
             self.sync_lines([line])
 
     def bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self.k + self.v)
+        return sum(t.numel() * t.element_size() for t in self._tensors())

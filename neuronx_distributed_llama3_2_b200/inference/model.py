@@ -25,12 +25,14 @@ import torch.nn as nn
 
 from ..models.llama import LlamaConfig, LlamaForCausalLM
 from ..models.dbrx import DbrxConfig, DbrxForCausalLM
+from ..models.gekazen import GekazenConfig, GekazenForCausalLM
 from ..models.mixtral import MixtralConfig, MixtralForCausalLM
 from ..ops import activation as act_ops
 from ..ops import attention as attn_ops
 from ..ops import comm_linear
 from ..ops import norm as norm_ops
 from ..ops import rope as rope_ops
+from ..ops import window_attention as wa_ops
 from ..parallel import mappings
 from ..parallel import parallel_state as ps
 from .config import InferenceConfig
@@ -288,10 +290,14 @@ class KVCacheInferenceMixin:
     @torch.no_grad()
     def forward_infer(self, input_ids: torch.Tensor, position_ids: torch.Tensor, seq_ids: Optional[torch.Tensor] = None,
                       last_token_index: Optional[torch.Tensor] = None, return_logits: bool = False,
-                      uniform: Optional[torch.Tensor] = None, return_hidden: bool = False):
+                      uniform: Optional[torch.Tensor] = None, return_hidden: bool = False,
+                      logit_index: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, sample: bool = True):
         """``input_ids [B, T]``; ``position_ids [B, T]`` absolute positions; ``seq_ids [B]`` cache lines (default
         ``arange(B)``); ``last_token_index [B]`` index (within T) of the last real prompt token (context encoding with
-        right padding).  Returns sampled tokens ``[B]`` (and the ``[B, V]`` logits with ``return_logits``)."""
+        right padding).  Returns sampled tokens ``[B]`` (and the ``[B, V]`` logits with ``return_logits``).
+        ``logit_index = (rows, cols)``: logits are computed at those ``N`` (row, token) places instead of the last
+        token of every row (scoring a prompt, replaying a trace) -> ``[N, V]``; ``sample=False`` skips the sampler and
+        returns ``None`` for the tokens."""
         assert self.kv_cache is not None, "call init_kv_cache() first"
         B, T = input_ids.shape
         prefill = T > 1
@@ -299,6 +305,9 @@ class KVCacheInferenceMixin:
         # replayed with the same static tensor objects but new contents, so the conversion has to be part of every
         # forward (and of every capture)
         self._decode_i32_memo = None
+        # how many of the T rows are real tokens (right padding), for layers that must not write padding into the cache
+        self._step_new_tokens = ((last_token_index + 1).to(torch.int32) if (prefill and last_token_index is not None)
+                                 else None)
         default_lines = seq_ids is None
         hidden = self._embed(input_ids)
         lengths = (position_ids[:, -1] + 1).to(torch.int32)
@@ -310,18 +319,23 @@ class KVCacheInferenceMixin:
             seq_ids if seq_ids is not None else torch.arange(B, device=input_ids.device, dtype=torch.int32))
         for i, layer in enumerate(self._decoder_layers()):
             hidden, residual = self._layer(i, layer, hidden, residual, position_ids, sid, lengths, prefill)
-        if prefill:
+        if logit_index is not None:
+            rows, cols = logit_index[0].long(), logit_index[1].long()
+            hidden, residual = hidden[rows, cols], (residual[rows, cols] if residual is not None else None)
+        elif prefill:
             idx = last_token_index if last_token_index is not None else torch.full((B,), T - 1, device=hidden.device)
             rows = torch.arange(B, device=hidden.device)
-            hidden, residual = hidden[rows, idx.long()], residual[rows, idx.long()]
+            hidden, residual = hidden[rows, idx.long()], (residual[rows, idx.long()] if residual is not None else None)
         else:
             hidden, residual = hidden[:, 0], (residual[:, 0] if residual is not None else None)
         hidden, _ = self._add_norm(self._final_norm(), hidden.contiguous(),
                                    residual.contiguous() if residual is not None else None)
         logits = self.lm_head(hidden)                                   # [B, V/tp]
         logits = mappings.gather_from_tensor_model_parallel_region(logits)[:, : self.config.vocab_size]
-        tokens = self.sampler.sample(logits.float() if logits.dtype not in (torch.float32, torch.bfloat16) else logits,
-                                     uniform)
+        tokens = None
+        if sample:
+            tokens = self.sampler.sample(logits.float() if logits.dtype not in (torch.float32, torch.bfloat16) else logits,
+                                         uniform)
         if return_hidden:                  # final-norm output of the selected position: what extra heads (Medusa) read
             return tokens, logits, hidden
         return (tokens, logits) if return_logits else tokens
@@ -462,3 +476,78 @@ class DbrxInferenceModel(_MoEDecoderLayout, KVCacheInferenceMixin, DbrxForCausal
     def _add_norm(self, norm, hidden: torch.Tensor, residual: Optional[torch.Tensor]):
         summed = hidden if residual is None else hidden + residual
         return norm(summed), summed
+
+
+class GekazenInferenceModel(KVCacheInferenceMixin, GekazenForCausalLM):
+    """Gekazen over the KV cache.  The step function, cache manager, last-token / indexed logits and sampler are the
+    mixin's; the family overrides what a layer does with the stream:
+
+      * ``hidden`` is the fp32 residual stream, ``residual`` its copy rounded to the activation dtype (what the matrix
+        products read) -- both come out of the post-norm kernel in one pass;
+      * a layer = fused q|k|v projection (+ bias) -> unit-RMS q / k and the cache write in one kernel -> windowed
+        attention over the cache (prefill tile kernel or decode kernel) -> output projection -> ``x += norm1(.)`` ->
+        sparse mixture -> ``x += norm2(.)``;
+      * the cache holds per-layer shapes, and layers with ``kv_from`` own no cache tensors (``KVCache.share_from``).
+    A step may start at any position (``position_ids[:, 0]``): the prefill kernel reads all earlier keys from the cache.
+    """
+
+    supports_prefill_at_offset = True
+
+    def __init__(self, config: GekazenConfig, inference_config: Optional[InferenceConfig] = None, device=None):
+        GekazenForCausalLM.__init__(self, config, device=device)
+        self._init_inference(inference_config)
+
+    def _decoder_layers(self):
+        return self.layers
+
+    def _embedding(self):
+        return self.embed_tokens
+
+    def _final_norm(self):
+        return self.norm
+
+    def init_kv_cache(self, device=None, dtype=None) -> KVCache:
+        ic, cfg = self.inference_config, self.config
+        device = device or next(self.parameters()).device
+        specs = [(L.mixer.kv_heads, L.mixer.dim, L.mixer.vdim) for L in cfg.layers]
+        share = {i: L.mixer.kv_from for i, L in enumerate(cfg.layers) if L.mixer.kv_from is not None}
+        self.kv_cache = KVCache(len(cfg.layers), ic.max_batch_size, 0, ic.seq_len, 0, dtype=dtype or cfg.torch_dtype,
+                                device=device, paged=ic.paged_kv, page_size=ic.page_size,
+                                num_pages=ic.num_kv_pages if ic.paged_kv else None, layer_specs=specs, share_from=share)
+        return self.kv_cache
+
+    def _embed(self, input_ids: torch.Tensor) -> torch.Tensor:
+        return super()._embed(input_ids).float()           # the stream is fp32 from the first layer on
+
+    def _add_norm(self, norm, hidden: torch.Tensor, residual: Optional[torch.Tensor]):
+        """Only the model's final norm comes through here: plain norm of the fp32 stream."""
+        return norm(hidden, out_dtype=self.config.torch_dtype), None
+
+    def _layer(self, i: int, layer, hidden, residual, positions, seq_ids, lengths, prefill):
+        cfg, dt = self.config, self.config.torch_dtype
+        B, T, W = hidden.shape
+        x = hidden if hidden.is_contiguous() else hidden.contiguous()
+        h = residual if residual is not None else x.to(dt)
+        attn, m = layer.self_attn, layer.self_attn.cfg
+        kc = self.kv_cache
+        ck, cv = kc.layer(i)
+        owns = kc.owns(i)
+        paged = dict(block_table=kc.block_table, page_size=kc.page_size) if kc.paged else {}
+        q_start = positions[:, 0]
+        n_new = self._step_new_tokens if prefill else None
+        q = wa_ops.qk_norm_cache_write(attn.qkv_proj(h), ck if owns else None, cv if owns else None, q_start, m.heads,
+                                       m.kv_heads, m.dim, m.vdim, cfg.rms_norm_eps, n_new=n_new, seq_ids=seq_ids, **paged)
+        if T == 1:
+            o = wa_ops.window_attention_decode(q[:, 0], ck, cv, q_start, m.scale, m.window, m.keep_first, attn.slopes,
+                                               seq_ids=seq_ids, **paged)
+        else:
+            o = wa_ops.window_attention_prefill(q, ck, cv, q_start, m.scale, m.window, m.keep_first, attn.slopes,
+                                                n_new=n_new, seq_ids=seq_ids, **paged)
+        x, h = layer.norm1.add_to(x, attn.o_proj(o.reshape(B, T, m.heads * m.vdim)), dt)
+        if layer.mlp is not None:
+            y = layer.mlp(h.reshape(B * T, W))
+            x, h = layer.norm2.add_to(x, y.reshape(B, T, W), dt)
+        return x, h
+
+    def forward_speculation(self, *a, **kw):
+        raise NotImplementedError("the speculation verify graph is not wired for this family")

@@ -1,0 +1,118 @@
+"""Model registry: which configuration class, inference model and checkpoint converter serve a ``config.json``.
+
+A family registers a predicate on the parsed ``config.json`` plus three callables; ``load_model(dir)`` then builds the
+inference model of whatever family the directory holds, loads ``model.safetensors`` (or any other format
+``inference.checkpoint.load_state_dict`` reads) through the family's converter and allocates the KV cache.  The runner
+classes, the trace replayer and the examples pick their model class here instead of hard-coding it.
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, List, Optional
+
+import torch
+
+from .config import InferenceConfig
+
+
+@dataclass
+class ModelFamily:
+    name: str
+    matches: Callable[[Dict[str, Any]], bool]
+    make_config: Callable[[Dict[str, Any], torch.dtype], Any]
+    model_cls: Callable[[], type]                                   # lazy: importing a family costs nothing until used
+    convert_state_dict: Callable[[Dict[str, torch.Tensor], Any], Dict[str, torch.Tensor]]
+
+
+_FAMILIES: List[ModelFamily] = []
+
+
+def register_family(family: ModelFamily) -> None:
+    _FAMILIES[:] = [f for f in _FAMILIES if f.name != family.name] + [family]
+
+
+def families() -> List[str]:
+    return [f.name for f in _FAMILIES]
+
+
+def resolve(config: Dict[str, Any]) -> ModelFamily:
+    for fam in _FAMILIES:
+        if fam.matches(config):
+            return fam
+    raise ValueError(f"no registered model family serves this config.json (keys {sorted(config)[:8]}; "
+                     f"families: {families()})")
+
+
+def _arch(config: Dict[str, Any]) -> str:
+    a = config.get("architecture") or (config.get("architectures") or [""])[0] or config.get("model_type") or ""
+    return str(a).lower()
+
+
+def _llama_config(d, dtype):
+    from ..models.llama import config_from_hf_json
+
+    return config_from_hf_json(d, torch_dtype=dtype, sequence_parallel_enabled=False)
+
+
+def _llama_convert(sd, cfg):
+    from ..scripts.checkpoint_converter import CheckpointConverterBase
+
+    return CheckpointConverterBase(cfg.num_hidden_layers, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
+                                   tie_word_embeddings=cfg.tie_word_embeddings).hf_to_nxd_full(sd)
+
+
+def _llama_cls():
+    from .model import LlamaInferenceModel
+
+    return LlamaInferenceModel
+
+
+def _gekazen_config(d, dtype):
+    from ..models.gekazen import GekazenConfig
+
+    return GekazenConfig.from_dict(d, torch_dtype=dtype)
+
+
+def _gekazen_convert(sd, cfg):
+    from ..models.gekazen import convert_gekazen_state_dict
+
+    return convert_gekazen_state_dict(sd, cfg)
+
+
+def _gekazen_cls():
+    from .model import GekazenInferenceModel
+
+    return GekazenInferenceModel
+
+
+register_family(ModelFamily("llama", lambda c: _arch(c).startswith("llama"), _llama_config, _llama_cls, _llama_convert))
+register_family(ModelFamily("gekazen", lambda c: _arch(c) == "gekazen", _gekazen_config, _gekazen_cls, _gekazen_convert))
+
+
+def read_config(model_dir: str) -> Dict[str, Any]:
+    with open(os.path.join(model_dir, "config.json")) as f:
+        return json.load(f)
+
+
+def load_model(model_dir: str, dtype: torch.dtype = torch.bfloat16, inference_config: Optional[InferenceConfig] = None,
+               device=None, load_weights: bool = True):
+    """The inference model of the family that ``model_dir/config.json`` names, with weights and KV cache."""
+    from .checkpoint import load_state_dict
+
+    raw = read_config(model_dir)
+    fam = resolve(raw)
+    cfg = fam.make_config(raw, dtype)
+    device = device or (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available()
+                        else torch.device("cpu"))
+    model = fam.model_cls()(cfg, inference_config, device=device)
+    if load_weights:
+        sd = fam.convert_state_dict(load_state_dict(model_dir), cfg)
+        missing, unexpected = model.load_state_dict(sd, strict=False)
+        missing = [k for k in missing if not k.endswith("slopes")]
+        if missing or unexpected:
+            raise KeyError(f"{fam.name}: checkpoint does not fit the model (missing {missing[:4]}, "
+                           f"unexpected {list(unexpected)[:4]})")
+    model.init_kv_cache(device=device)
+    return model

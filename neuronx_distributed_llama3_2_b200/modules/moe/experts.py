@@ -79,11 +79,14 @@ class _GemmCombine(torch.autograd.Function):
 class Experts(torch.nn.Module):
     def __init__(self, num_experts: int, hidden_size: int, intermediate_size: int, glu: bool,
                  activation_fn: Callable[[torch.Tensor], torch.Tensor], dtype: torch.dtype = torch.float32, device=None,
-                 input_layer_init_method=None, output_layer_init_method=None):
+                 input_layer_init_method=None, output_layer_init_method=None,
+                 glu_fn: Optional[Callable[[torch.Tensor], torch.Tensor]] = None):
         super().__init__()
         self.num_experts = num_experts
         self.glu = glu
         self.activation_fn = activation_fn
+        # gated activations that are not ``act(gate) * up`` (clamped / shifted forms) take the fused (gate | up) tensor
+        self.glu_fn = glu_fn
         self.intermediate_size = intermediate_size
         ep = ps.get_expert_model_parallel_size()
         if glu:  # gate | up fused on the output dim, sharded with stride 2 like the dense MLP
@@ -109,8 +112,11 @@ class Experts(torch.nn.Module):
             hidden_states = mappings.enter_expert_parallel_region(hidden_states)   # (E/ep, ep, C, H)
         if self.glu:
             gu = self.gate_up_proj(hidden_states, expert_indices)
-            gate, up = torch.chunk(gu, 2, dim=-1)
-            inter = self.activation_fn(gate) * up
+            if self.glu_fn is not None:
+                inter = self.glu_fn(gu)
+            else:
+                gate, up = torch.chunk(gu, 2, dim=-1)
+                inter = self.activation_fn(gate) * up
         else:
             inter = self.activation_fn(self.up_proj(hidden_states, expert_indices))
         out = self.down_proj(inter, expert_indices)

@@ -101,3 +101,36 @@ class RouterSinkhorn(RouterBase):
         else:
             expert_index = torch.argmax(router_logits, dim=1, keepdim=True)
         return router_logits, expert_affinities.to(hidden_states.dtype), expert_index.detach().to(torch.long)
+
+
+class RouterBiasedTopK(RouterBase):
+    """Softmax scores over ``num_experts + num_identity_experts`` router outputs; the CHOICE of the ``top_k`` experts is
+    made on ``score + correction`` (a per-expert bias that steers load without entering the output), the combination
+    weights are the chosen experts' plain scores times ``affinity_scale``, not renormalised.  The last
+    ``num_identity_experts`` outputs are identity experts (their output is their input; they have no weights).  The
+    router runs in fp32 whatever the activation dtype; ``select`` is the fused device path (one kernel: projection,
+    softmax, choice, optional sigmoid gate of a shared expert)."""
+
+    def __init__(self, num_experts: int, top_k: int, hidden_size: int, num_identity_experts: int = 0,
+                 affinity_scale: float = 1.0, device: torch.device = torch.device("cpu")):
+        super().__init__(num_experts + num_identity_experts, top_k, hidden_size, "softmax", torch.float32, device)
+        self.num_real_experts = num_experts
+        self.num_identity_experts = num_identity_experts
+        self.affinity_scale = affinity_scale
+        self.correction = torch.nn.Parameter(torch.zeros(num_experts + num_identity_experts, dtype=torch.float32,
+                                                         device=device), requires_grad=False)
+
+    def select(self, hidden_states: torch.Tensor, shared_gate_weight=None):
+        """``(expert_index [T, k] int32, weights [T, k] fp32, shared gate [T] fp32 or None)``."""
+        from ...ops import moe_sparse
+
+        flat = hidden_states.reshape(-1, hidden_states.shape[-1])
+        return moe_sparse.route(flat, self.linear_router.weight, self.correction, self.top_k, self.affinity_scale,
+                                shared_gate_weight)
+
+    def forward(self, hidden_states):
+        flat = hidden_states.reshape(-1, hidden_states.shape[-1])
+        router_logits = flat.float() @ self.linear_router.weight.float().t()
+        scores = self.apply_activation_fn(router_logits)
+        _, expert_index = torch.topk(scores + self.correction.float(), self.top_k, dim=1)
+        return router_logits, scores * self.affinity_scale, expert_index.detach().to(torch.long)

@@ -38,7 +38,15 @@ NVCC_FLAGS = [
     "-Xptxas", "-v",
 ] + [f for f in os.environ.get("NXD_NVCC_EXTRA", "").split() if f]
 
+# Kernel groups: a model family whose kernels live in a few sources of their own can be served from a small library
+# built from just those sources (plus the runtime helpers), so a fresh checkout compiles only what that family needs.
+# When the full library is already built it contains every group and is used instead.
+GROUPS = {
+    "window_moe": ["window_attention.cu", "post_norm.cu", "moe_sparse.cu", "runtime.cu"],
+}
+
 _lib: Optional[ctypes.CDLL] = None
+_group_libs = {}
 _lock = threading.Lock()
 launch_count = 0  # number of our kernels' entry points invoked (bench "gpu_launches")
 
@@ -54,22 +62,34 @@ def sources() -> List[str]:
     return sorted(glob.glob(os.path.join(CSRC_DIR, "*.cu")))
 
 
-def _stale() -> bool:
-    if not os.path.exists(LIB_PATH):
+def group_sources(group: str) -> List[str]:
+    return [os.path.join(CSRC_DIR, f) for f in GROUPS[group]]
+
+
+def group_lib_path(group: str) -> str:
+    return os.path.join(_HERE, f"libnxd_b200_{group}.so")
+
+
+def _stale(group: Optional[str] = None) -> bool:
+    path = group_lib_path(group) if group else LIB_PATH
+    if not os.path.exists(path):
         return True
-    t = os.path.getmtime(LIB_PATH)
-    deps = sources() + glob.glob(os.path.join(CSRC_DIR, "*.cuh")) + glob.glob(os.path.join(INCLUDE_DIR, "*.h"))
+    t = os.path.getmtime(path)
+    deps = ((group_sources(group) if group else sources()) + glob.glob(os.path.join(CSRC_DIR, "*.cuh"))
+            + glob.glob(os.path.join(INCLUDE_DIR, "*.h")))
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile every ``csrc/*.cu`` for sm_100a and link ``libnxd_b200.so`` in-tree.
+def build(force: bool = False, verbose: bool = False, group: Optional[str] = None) -> str:
+    """Compile every ``csrc/*.cu`` for sm_100a and link ``libnxd_b200.so`` in-tree; with ``group`` only that group's
+    sources, linked as ``libnxd_b200_<group>.so``.
 
     Works without a GPU (nvcc cross-compiles).  Per-file objects are cached under
     ``build/obj`` and rebuilt only when the source (or any header) is newer.
     """
-    if not force and not _stale():
-        return LIB_PATH
+    out_path = group_lib_path(group) if group else LIB_PATH
+    if not force and not _stale(group):
+        return out_path
     os.makedirs(BUILD_DIR, exist_ok=True)
     hdrs = glob.glob(os.path.join(CSRC_DIR, "*.cuh")) + glob.glob(os.path.join(INCLUDE_DIR, "*.h"))
     hdr_time = max([os.path.getmtime(h) for h in hdrs], default=0.0)
@@ -89,25 +109,37 @@ def build(force: bool = False, verbose: bool = False) -> str:
         return obj
 
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
-        objs = list(ex.map(compile_one, sources()))
-    cmd = [nvcc, "-shared", "-o", LIB_PATH] + objs + ["-lcudart"]
+        objs = list(ex.map(compile_one, group_sources(group) if group else sources()))
+    tmp = out_path + f".tmp{os.getpid()}"
+    cmd = [nvcc, "-shared", "-o", tmp] + objs + ["-lcudart"]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+    os.replace(tmp, out_path)
     if logs:
-        with open(os.path.join(BUILD_DIR, "ptxas_v.log"), "w") as f:
+        with open(os.path.join(BUILD_DIR, f"ptxas_v_{group}.log" if group else "ptxas_v.log"), "w") as f:
             for src, text in logs.items():
                 f.write(f"==== {os.path.basename(src)}\n{text}\n")
     if verbose:
         for src, text in logs.items():
             sys.stderr.write(f"==== {src}\n{text}\n")
-    return LIB_PATH
+    return out_path
 
 
-def lib() -> ctypes.CDLL:
+def lib(group: Optional[str] = None) -> ctypes.CDLL:
+    """The kernel library.  ``group``: a library that holds at least that kernel group -- the full one when it is
+    loaded or built and current, else the group's own small library (built on first use)."""
     global _lib
     if _lib is not None:
         return _lib
+    if group is not None and "NXD_B200_LIB" not in os.environ and _stale():
+        with _lock:
+            handle = _group_libs.get(group)
+            if handle is None:
+                handle = ctypes.CDLL(build(group=group))
+                handle.nxd_last_error.restype = ctypes.c_char_p
+                _group_libs[group] = handle
+        return handle
     with _lock:
         if _lib is None:
             if not os.path.exists(LIB_PATH):
@@ -118,14 +150,14 @@ def lib() -> ctypes.CDLL:
     return _lib
 
 
-def available() -> bool:
+def available(group: Optional[str] = None) -> bool:
     """True when our CUDA kernels are usable (a GPU is present and the .so loads)."""
     if not torch.cuda.is_available():
         return False
     if os.environ.get("NXD_FORCE_TORCH", "0") == "1":
         return False
     try:
-        lib()
+        lib(group)
         return True
     except Exception as e:
         if os.environ.get("NXD_ALLOW_TORCH_FALLBACK", "0") == "1":
@@ -138,20 +170,23 @@ def available() -> bool:
 
 def kernel_launches() -> int:
     """Kernel launches made by the library in this process so far (counted at every ``<<<>>>`` in csrc/)."""
-    fn = lib().nxd_kernel_launches
-    fn.restype = ctypes.c_ulonglong
-    return int(fn())
+    total = 0
+    for handle in ([_lib] if _lib is not None else []) + list(_group_libs.values()) or [lib()]:
+        fn = handle.nxd_kernel_launches
+        fn.restype = ctypes.c_ulonglong
+        total += int(fn())
+    return total
 
 
 def stream_ptr() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def check(code: int, what: str) -> None:
+def check(code: int, what: str, handle: Optional[ctypes.CDLL] = None) -> None:
     global launch_count
     launch_count += 1
     if code != 0:
-        msg = lib().nxd_last_error()
+        msg = (handle or lib()).nxd_last_error()
         raise RuntimeError(f"{what} failed (code {code}): {msg.decode() if msg else ''}")
 
 

@@ -87,3 +87,53 @@ def fused_add_rms_norm(x: torch.Tensor, residual: torch.Tensor, w: torch.Tensor,
         return _RMSNormFn.apply(x, w, eps, residual)
     s = x + residual
     return rms_norm_ref(s, w, eps), s
+
+
+# ---- norm on a sublayer's OUTPUT, added to an fp32 residual stream (``csrc/post_norm.cu``) ---------------------------
+_POST_GROUP = "window_moe"
+
+
+def _post_code(dtype: torch.dtype) -> int:
+    return {torch.bfloat16: 0, torch.float32: 1}[dtype]
+
+
+def post_norm_residual_(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype = None,
+                        offset: float = 1.0):
+    """``x += y / sqrt(mean(y^2) + eps) * (offset + w)`` in place on the fp32 stream ``x``; returns ``(x, x.to(out_dtype))``
+    (the rounded copy that the next sublayer's matrix products read; ``None`` without ``out_dtype``).  With
+    ``offset = 1`` the weight is stored around zero."""
+    assert x.dtype == torch.float32 and x.shape == y.shape
+    W = x.shape[-1]
+    if x.is_cuda and y.dtype in (torch.bfloat16, torch.float32) and _lib.available(_POST_GROUP):
+        assert x.is_contiguous()
+        y2 = y if y.is_contiguous() else y.contiguous()
+        wc = w if w.dtype in (torch.bfloat16, torch.float32) else w.float()
+        h = torch.empty(x.shape, dtype=out_dtype, device=x.device) if out_dtype is not None else None
+        L = _lib.lib(_POST_GROUP)
+        rc = L.nxd_post_norm_residual(_c.c_int(_post_code(y2.dtype)), _c.c_int(_post_code(wc.dtype)),
+                                      _c.c_int(_post_code(out_dtype) if out_dtype is not None else 1), _lib.ptr(y2),
+                                      _lib.ptr(wc), _lib.ptr(x), _lib.ptr(h), _c.c_longlong(x.numel() // W), _c.c_int(W),
+                                      _c.c_float(eps), _c.c_float(offset), _lib.stream_ptr())
+        _lib.check(rc, "nxd_post_norm_residual", L)
+        return x, h
+    yf = y.float()
+    x.add_(yf / torch.sqrt(yf.pow(2).mean(-1, keepdim=True) + eps) * (offset + w.float()))
+    return x, (x.to(out_dtype) if out_dtype is not None else None)
+
+
+def rms_norm_offset(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype, offset: float = 1.0) -> torch.Tensor:
+    """``x / sqrt(mean(x^2) + eps) * (offset + w)`` with fp32 statistics, result in ``out_dtype``."""
+    W = x.shape[-1]
+    if x.is_cuda and x.dtype in (torch.bfloat16, torch.float32) and _lib.available(_POST_GROUP):
+        x2 = x if x.is_contiguous() else x.contiguous()
+        wc = w if w.dtype in (torch.bfloat16, torch.float32) else w.float()
+        h = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        L = _lib.lib(_POST_GROUP)
+        rc = L.nxd_post_norm_residual(_c.c_int(_post_code(x2.dtype)), _c.c_int(_post_code(wc.dtype)),
+                                      _c.c_int(_post_code(out_dtype)), _lib.ptr(x2), _lib.ptr(wc), _lib.ptr(None),
+                                      _lib.ptr(h), _c.c_longlong(x.numel() // W), _c.c_int(W), _c.c_float(eps),
+                                      _c.c_float(offset), _lib.stream_ptr())
+        _lib.check(rc, "nxd_post_norm_residual", L)
+        return h
+    xf = x.float()
+    return (xf / torch.sqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * (offset + w.float())).to(out_dtype)

@@ -1,0 +1,203 @@
+"""Attention over the KV cache with a sliding window, kept first tokens and a linear distance bias
+(``csrc/window_attention.cu``), next to the plain causal ops of ``ops/attention.py``.
+
+    visible(i, j) = j <= i and (window is None or i - j < window or j < keep_first)
+    score(i, j)   = scale * <q_i, k_j> - slope_h * (i - j)
+
+Head sizes are free (query/key size ``D`` and value size ``Dv`` may differ); activations and cache are bf16 or fp32, the
+softmax and the unit-RMS normalisation of queries and keys run in fp32.  The prefill op reads keys and values from the
+cache, so a step may start at any position of a sequence (``q_start``), and the same entry points serve a contiguous
+cache ``[lines, G, S, D]`` and a paged one ``[pages, G, page, D]`` + block table.
+
+Every op has a plain PyTorch restatement used on CPU (and as the oracle of the kernel tests).
+"""
+from __future__ import annotations
+
+import ctypes as _c
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+GROUP = "window_moe"
+
+
+def _code(dtype: torch.dtype) -> int:
+    return {torch.bfloat16: 0, torch.float32: 1}[dtype]
+
+
+def _use_kernel(x: torch.Tensor) -> bool:
+    return x.is_cuda and x.dtype in (torch.bfloat16, torch.float32) and _lib.available(GROUP)
+
+
+def _i32(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    if t is None:
+        return None
+    return t if (t.dtype == torch.int32 and t.is_contiguous()) else t.to(torch.int32).contiguous()
+
+
+def distance_slopes(n_heads: int, exponent: float = 8.0, device=None) -> torch.Tensor:
+    """Geometric per-head slopes ``2 ** (-exponent * (h + 1) / n_heads)`` of the linear distance bias, fp32 ``[H]``."""
+    h = torch.arange(1, n_heads + 1, dtype=torch.float64)
+    return torch.pow(2.0, -exponent * h / n_heads).to(torch.float32).to(device)
+
+
+def _cache_rows(cache: torch.Tensor, line: int, n: int, block_table, page_size: int) -> torch.Tensor:
+    """Rows ``[0, n)`` of a cache line as ``[G, n, D]``."""
+    if block_table is None:
+        return cache[line, :, :n]
+    pages = block_table[line, : (n + page_size - 1) // page_size].long()
+    return cache[pages].permute(1, 0, 2, 3).reshape(cache.shape[1], -1, cache.shape[3])[:, :n]
+
+
+def _cache_args(cache_k, cache_v, block_table, page_size):
+    bt = _i32(block_table)
+    return (_c.c_longlong(cache_k.stride(0)), _c.c_longlong(cache_k.stride(1)), _c.c_longlong(cache_v.stride(0)),
+            _c.c_longlong(cache_v.stride(1)), _lib.ptr(bt), _c.c_int(page_size if bt is not None else 0),
+            _c.c_int(bt.shape[1] if bt is not None else 0)), bt
+
+
+def qk_norm_cache_write(qkv: torch.Tensor, cache_k: Optional[torch.Tensor], cache_v: Optional[torch.Tensor],
+                        q_start: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int, eps: float,
+                        n_new: Optional[torch.Tensor] = None, seq_ids: Optional[torch.Tensor] = None,
+                        normalize: bool = True, block_table: Optional[torch.Tensor] = None,
+                        page_size: int = 0) -> torch.Tensor:
+    """``qkv [B, T, heads*dim (+ kv_heads*dim + kv_heads*vdim)]`` -> ``q [B, T, heads, dim]``; with a cache given the
+    key and value heads of the real rows (``t < n_new[b]``) are written at position ``q_start[b] + t`` of cache line
+    ``seq_ids[b]``.  ``normalize``: queries and keys are divided by their root mean square over ``dim`` (fp32, ``eps``
+    inside the root) before they are written."""
+    B, T, n_out = qkv.shape
+    has_kv = cache_k is not None
+    assert n_out == heads * dim + (kv_heads * (dim + vdim) if has_kv else 0), (n_out, heads, kv_heads, dim, vdim)
+    if _use_kernel(qkv):
+        qkv = qkv if qkv.is_contiguous() else qkv.contiguous()
+        q = torch.empty(B, T, heads, dim, dtype=qkv.dtype, device=qkv.device)
+        qs, nn_, sid = _i32(q_start), _i32(n_new), _i32(seq_ids)
+        ck = cache_k if has_kv else q
+        cv = cache_v if has_kv else q
+        cargs, bt = _cache_args(ck, cv, block_table if has_kv else None, page_size)
+        max_pos = (bt.shape[1] * page_size if bt is not None else ck.shape[2]) if has_kv else 0
+        L = _lib.lib(GROUP)
+        rc = L.nxd_qk_norm_cache_write(_c.c_int(_code(qkv.dtype)), _lib.ptr(qkv), _c.c_longlong(n_out), _lib.ptr(q),
+                                       _lib.ptr(ck), _lib.ptr(cv), *cargs, _lib.ptr(qs), _lib.ptr(nn_), _lib.ptr(sid),
+                                       _c.c_int(B), _c.c_int(T), _c.c_int(heads), _c.c_int(kv_heads), _c.c_int(dim),
+                                       _c.c_int(vdim), _c.c_int(int(has_kv)), _c.c_int(int(normalize)), _c.c_float(eps),
+                                       _c.c_int(max_pos), _lib.stream_ptr())
+        _lib.check(rc, "nxd_qk_norm_cache_write", L)
+        return q
+
+    def unit(x):
+        if not normalize:
+            return x
+        xf = x.float()
+        return (xf / torch.sqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)
+
+    q = unit(qkv[..., : heads * dim].reshape(B, T, heads, dim))
+    if has_kv:
+        k = unit(qkv[..., heads * dim: (heads + kv_heads) * dim].reshape(B, T, kv_heads, dim))
+        v = qkv[..., (heads + kv_heads) * dim:].reshape(B, T, kv_heads, vdim)
+        for b in range(B):
+            n = T if n_new is None else int(n_new[b])
+            line = b if seq_ids is None else int(seq_ids[b])
+            p0 = int(q_start[b])
+            for t in range(n):
+                pos = p0 + t
+                if block_table is not None:
+                    page, off = int(block_table[line, pos // page_size]), pos % page_size
+                    cache_k[page, :, off] = k[b, t]
+                    cache_v[page, :, off] = v[b, t]
+                else:
+                    cache_k[line, :, pos] = k[b, t]
+                    cache_v[line, :, pos] = v[b, t]
+    return q.contiguous()
+
+
+def window_attention_ref(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_pos: torch.Tensor, scale: float,
+                         window: Optional[int], keep_first: int, slopes: Optional[torch.Tensor]) -> torch.Tensor:
+    """One sequence in fp32: ``q [Tq, H, D]`` at positions ``q_pos [Tq]`` over keys ``k [G, Tk, D]`` / ``v [G, Tk, Dv]``
+    at positions ``0 .. Tk - 1``."""
+    H, G = q.shape[1], k.shape[0]
+    kf = k.float().repeat_interleave(H // G, dim=0)
+    vf = v.float().repeat_interleave(H // G, dim=0)
+    s = torch.einsum("qhd,hkd->hqk", q.float(), kf) * scale
+    j = torch.arange(k.shape[1], device=q.device)
+    dist = (q_pos.reshape(-1, 1) - j.reshape(1, -1))                      # [Tq, Tk]
+    vis = dist >= 0
+    if window is not None and window > 0:
+        vis = vis & ((dist < window) | (j.reshape(1, -1) < keep_first))
+    if slopes is not None:
+        s = s - slopes.float().reshape(H, 1, 1) * dist.float()
+    s = s.masked_fill(~vis, float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    p = torch.nan_to_num(p, nan=0.0)                                      # a row that sees nothing
+    return torch.einsum("hqk,hkd->qhd", p, vf)
+
+
+def window_attention_prefill(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor, q_start: torch.Tensor,
+                             scale: float, window: Optional[int] = None, keep_first: int = 0,
+                             slopes: Optional[torch.Tensor] = None, n_new: Optional[torch.Tensor] = None,
+                             seq_ids: Optional[torch.Tensor] = None, block_table: Optional[torch.Tensor] = None,
+                             page_size: int = 0) -> torch.Tensor:
+    """``q [B, T, H, D]``: new tokens of every row at positions ``q_start[b] + t`` (their keys / values already in the
+    cache) -> ``[B, T, H, Dv]``.  Rows ``t >= n_new[b]`` are padding and come out as zeros."""
+    B, T, H, D = q.shape
+    G, Dv = cache_k.shape[1], cache_v.shape[3]
+    w = int(window) if window else 0
+    if _use_kernel(q):
+        q = q if q.is_contiguous() else q.contiguous()
+        out = torch.empty(B, T, H, Dv, dtype=q.dtype, device=q.device)
+        qs, nn_, sid = _i32(q_start), _i32(n_new), _i32(seq_ids)
+        cargs, bt = _cache_args(cache_k, cache_v, block_table, page_size)
+        L = _lib.lib(GROUP)
+        rc = L.nxd_window_attn_prefill(_c.c_int(_code(q.dtype)), _lib.ptr(q), _lib.ptr(cache_k), _lib.ptr(cache_v),
+                                       *cargs, _lib.ptr(out), _lib.ptr(qs), _lib.ptr(nn_), _lib.ptr(sid),
+                                       _lib.ptr(slopes), _c.c_int(B), _c.c_int(T), _c.c_int(H), _c.c_int(G), _c.c_int(D),
+                                       _c.c_int(Dv), _c.c_float(scale), _c.c_int(w), _c.c_int(keep_first),
+                                       _lib.stream_ptr())
+        _lib.check(rc, "nxd_window_attn_prefill", L)
+        return out
+    out = torch.zeros(B, T, H, Dv, dtype=q.dtype, device=q.device)
+    for b in range(B):
+        n = T if n_new is None else int(n_new[b])
+        if n == 0:
+            continue
+        line = b if seq_ids is None else int(seq_ids[b])
+        p0 = int(q_start[b])
+        kk = _cache_rows(cache_k, line, p0 + n, block_table, page_size)
+        vv = _cache_rows(cache_v, line, p0 + n, block_table, page_size)
+        pos = torch.arange(p0, p0 + n, device=q.device)
+        out[b, :n] = window_attention_ref(q[b, :n], kk, vv, pos, scale, w, keep_first, slopes).to(q.dtype)
+    return out
+
+
+def window_attention_decode(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor, positions: torch.Tensor,
+                            scale: float, window: Optional[int] = None, keep_first: int = 0,
+                            slopes: Optional[torch.Tensor] = None, seq_ids: Optional[torch.Tensor] = None,
+                            block_table: Optional[torch.Tensor] = None, page_size: int = 0) -> torch.Tensor:
+    """One new token per row: ``q [B, H, D]`` at ``positions[b]`` -> ``[B, H, Dv]``; only the kept first rows and the
+    window's rows of the cache line are read."""
+    B, H, D = q.shape
+    G, Dv = cache_k.shape[1], cache_v.shape[3]
+    w = int(window) if window else 0
+    if _use_kernel(q):
+        q = q if q.is_contiguous() else q.contiguous()
+        out = torch.empty(B, H, Dv, dtype=q.dtype, device=q.device)
+        pos, sid = _i32(positions), _i32(seq_ids)
+        cargs, bt = _cache_args(cache_k, cache_v, block_table, page_size)
+        L = _lib.lib(GROUP)
+        rc = L.nxd_window_attn_decode(_c.c_int(_code(q.dtype)), _lib.ptr(q), _lib.ptr(cache_k), _lib.ptr(cache_v), *cargs,
+                                      _lib.ptr(out), _lib.ptr(pos), _lib.ptr(sid), _lib.ptr(slopes), _c.c_int(B),
+                                      _c.c_int(H), _c.c_int(G), _c.c_int(D), _c.c_int(Dv), _c.c_float(scale), _c.c_int(w),
+                                      _c.c_int(keep_first), _lib.stream_ptr())
+        _lib.check(rc, "nxd_window_attn_decode", L)
+        return out
+    out = torch.empty(B, H, Dv, dtype=q.dtype, device=q.device)
+    for b in range(B):
+        line = b if seq_ids is None else int(seq_ids[b])
+        p = int(positions[b])
+        kk = _cache_rows(cache_k, line, p + 1, block_table, page_size)
+        vv = _cache_rows(cache_v, line, p + 1, block_table, page_size)
+        out[b] = window_attention_ref(q[b:b + 1], kk, vv, torch.tensor([p], device=q.device), scale, w, keep_first,
+                                      slopes)[0].to(q.dtype)
+    return out

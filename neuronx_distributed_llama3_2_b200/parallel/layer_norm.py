@@ -40,3 +40,21 @@ class RMSNorm(torch.nn.Module):
         if residual is not None:
             return norm_ops.fused_add_rms_norm(hidden_states, residual, self.weight, self.variance_epsilon)[0]
         return norm_ops.rms_norm(hidden_states, self.weight, self.variance_epsilon)
+
+
+class ZeroCenteredRMSNorm(torch.nn.Module):
+    """``x * rsqrt(mean(x^2) + eps) * (1 + w)``: the weight is stored around zero and kept in fp32; statistics in fp32.
+    ``forward`` is the plain norm (a model's final norm); ``add_to(x, y)`` is the post-norm residual update
+    ``x += norm(y)`` on an fp32 stream, returning the stream and its rounded copy."""
+
+    def __init__(self, hidden_size: int, eps: float = 1e-6, device=None):
+        super().__init__()
+        self.weight = torch.nn.Parameter(torch.zeros(hidden_size, dtype=torch.float32, device=device))
+        self.variance_epsilon = eps
+
+    def forward(self, hidden_states: torch.Tensor, out_dtype: torch.dtype = None) -> torch.Tensor:
+        return norm_ops.rms_norm_offset(hidden_states, self.weight, self.variance_epsilon,
+                                        out_dtype or hidden_states.dtype, offset=1.0)
+
+    def add_to(self, stream: torch.Tensor, sublayer_out: torch.Tensor, out_dtype: torch.dtype = None):
+        return norm_ops.post_norm_residual_(stream, sublayer_out, self.weight, self.variance_epsilon, out_dtype, offset=1.0)

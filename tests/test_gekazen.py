@@ -1,0 +1,388 @@
+"""Gekazen family against the float64 oracle of ``tests/gekazen_oracle.py``: every mechanism alone, then the model through
+the framework's step function, cache and schedulers.  Every test runs on the CPU (the ops' PyTorch path) and, marked
+``gpu``, on CUDA (the kernels) in fp32 and bf16."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import gekazen_oracle as O
+from neuronx_distributed_llama3_2_b200.inference import InferenceConfig
+from neuronx_distributed_llama3_2_b200.inference.model import GekazenInferenceModel
+from neuronx_distributed_llama3_2_b200.inference.trace_replay import TraceReplayer
+from neuronx_distributed_llama3_2_b200.models.gekazen import GekazenConfig, convert_gekazen_state_dict
+from neuronx_distributed_llama3_2_b200.ops import moe_sparse as ms
+from neuronx_distributed_llama3_2_b200.ops import norm as norm_ops
+from neuronx_distributed_llama3_2_b200.ops import window_attention as wa
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+F64 = torch.float64
+CASES = [("cpu", torch.float32), pytest.param("cuda", torch.float32, marks=pytest.mark.gpu),
+         pytest.param("cuda", torch.bfloat16, marks=pytest.mark.gpu)]
+case = pytest.mark.parametrize("dev,dt", CASES)
+
+
+def tol(dt):
+    return 2e-4 if dt == torch.float32 else 6e-2
+
+
+def close(a, b, dt, scale=1.0):
+    err = (a.detach().to("cpu", F64) - b.to(F64)).abs().max().item()
+    assert err <= tol(dt) * scale, f"max error {err:.3e} above {tol(dt) * scale:.1e}"
+
+
+def mixer(**kw):
+    m = dict(heads=4, kv_heads=2, dim=16, vdim=24, scale=0.2, mask={"size": 12, "keep_first": 3})
+    m.update(kw)
+    return m
+
+
+def mlp(**kw):
+    m = {"kind": "moe", "expert": {"ff": 32, "limit": 2.0},
+         "router": {"experts": 6, "identity": 1, "scale": 1.25, "top": 2}, "shared": {"ff": 40, "limit": 1.5}}
+    m.update(kw)
+    return m
+
+
+def config(layers=None, vocab=96, width=48):
+    layers = layers or [
+        {"type": "attention", "mixer": mixer(), "mlp": mlp()},
+        {"type": "attention", "mixer": mixer(mask={"size": 7, "keep_first": 0}), "mlp": None},
+        {"type": "attention", "mixer": mixer(kv_from=0, mask={"size": 20, "keep_first": 2}), "mlp": mlp(shared=None)},
+        {"type": "attention", "mixer": mixer(heads=2, kv_heads=2, dim=24, vdim=16), "mlp": mlp()},
+    ]
+    return {"architecture": "Gekazen", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": layers}
+
+
+# sizes that the usual configurations make equal or 1: one head, one expert chosen of few, no identity expert, no
+# shared expert, window of 1, everything kept, odd sizes
+ODD = config(layers=[
+    {"type": "attention", "mixer": mixer(heads=1, kv_heads=1, dim=10, vdim=6, mask={"size": 1, "keep_first": 0}),
+     "mlp": mlp(router={"experts": 2, "identity": 0, "scale": 1.0, "top": 1}, shared=None, expert={"ff": 9, "limit": 0.5})},
+    {"type": "attention", "mixer": mixer(heads=6, kv_heads=1, dim=8, vdim=8, mask={"size": 5, "keep_first": 9}),
+     "mlp": mlp(router={"experts": 3, "identity": 3, "scale": 0.5, "top": 4})},
+    {"type": "attention", "mixer": mixer(heads=3, kv_heads=3, dim=12, vdim=40, mask=None), "mlp": None},
+], vocab=50, width=30)
+
+
+def build(cfg, dev, dt, lines=4, seq_len=96, seed=0, paged=False, pages=None, page_size=8, sd=None):
+    sd = sd if sd is not None else O.random_weights(cfg, seed)
+    gc = GekazenConfig.from_dict(cfg, torch_dtype=dt)
+    ic = InferenceConfig(batch_size=lines, max_batch_size=lines, max_context_length=seq_len, seq_len=seq_len,
+                         is_continuous_batching=True, use_cuda_graphs=False, paged_kv=paged, page_size=page_size,
+                         num_kv_pages=pages)
+    model = GekazenInferenceModel(gc, ic, device=torch.device(dev))
+    missing, unexpected = model.load_state_dict(convert_gekazen_state_dict(sd, gc), strict=False)
+    assert not unexpected and all(k.endswith("slopes") for k in missing), (missing, unexpected)
+    model.init_kv_cache(device=torch.device(dev))
+    return model, sd
+
+
+def tokens_of(cfg, n, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, cfg["vocab"], (n,), generator=g).tolist()
+
+
+def replay(model, steps):
+    """steps: list of (entries, end); returns {request id: [logit rows in order]}."""
+    rp = TraceReplayer(model)
+    got = {}
+    for entries, end in steps:
+        out = rp.step(entries, end)
+        r = 0
+        for e in entries:
+            for _ in e["want"]:
+                got.setdefault(e["id"], []).append(out[r].cpu())
+                r += 1
+    return got
+
+
+def check_rows(rows, ref, places, dt):
+    for row, p in zip(rows, places):
+        d = row.to(F64) - ref[p]
+        d = d - d.mean()
+        rel = float(d.pow(2).mean().sqrt() / ref[p].std())
+        assert rel <= (2e-4 if dt == torch.float32 else 4e-2), f"position {p}: relative error {rel:.3e}"
+
+
+# ---- mechanisms alone ---------------------------------------------------------------------------------------------------
+@case
+def test_unit_norm_and_cache_write(dev, dt):
+    torch.manual_seed(1)
+    B, T, H, G, D, Dv, S = 2, 9, 4, 2, 10, 6, 16
+    qkv = torch.randn(B, T, H * D + G * (D + Dv))
+    ck, cv = torch.zeros(3, G, S, D, dtype=dt, device=dev), torch.zeros(3, G, S, Dv, dtype=dt, device=dev)
+    start, n_new, lines = torch.tensor([0, 4]), torch.tensor([9, 5]), torch.tensor([2, 0])
+    q = wa.qk_norm_cache_write(qkv.to(dev, dt), ck, cv, start.to(dev), H, G, D, Dv, 1e-5, n_new=n_new.to(dev),
+                               seq_ids=lines.to(dev))
+    x = qkv.to(dt).to(F64)
+    close(q, O.unit_rms(x[..., :H * D].reshape(B, T, H, D), 1e-5), dt)
+    k = O.unit_rms(x[..., H * D:(H + G) * D].reshape(B, T, G, D), 1e-5)
+    v = x[..., (H + G) * D:].reshape(B, T, G, Dv)
+    for b in range(B):
+        n, s, ln = int(n_new[b]), int(start[b]), int(lines[b])
+        close(ck[ln, :, s:s + n], k[b, :n].transpose(0, 1), dt)
+        close(cv[ln, :, s:s + n], v[b, :n].transpose(0, 1), dt)
+        assert float(ck[ln, :, s + n:].abs().sum()) == 0.0 and float(ck[ln, :, :s].abs().sum()) == 0.0   # padding unwritten
+    assert float(ck[1].abs().sum()) == 0.0
+
+
+def _planted(T, H, G, D, Dv, plant):
+    """Random q/k/v where, for every (query position, key position) in ``plant``, the key is made to stand out for that
+    query (aligned direction, large score) and carries a value far from the others -- a wrongly masked or wrongly
+    admitted key changes the output by O(1)."""
+    torch.manual_seed(7)
+    q, k, v = torch.randn(T, H, D) * 0.3, torch.randn(T, G, D) * 0.3, torch.randn(T, G, Dv)
+    for i, j in plant:
+        k[j] = q[i].reshape(G, H // G, D)[:, 0] * 40.0
+        v[j] = 25.0 + torch.randn(G, Dv)
+    return q, k, v
+
+
+@case
+@pytest.mark.parametrize("size,keep", [(12, 3), (33, 0), (1, 2), (None, 0), (64, 5)])
+def test_window_attention_prefill_and_decode_edges(dev, dt, size, keep):
+    T, H, G, D, Dv, scale = 80, 4, 2, 16, 24, 0.25
+    w = size if size is not None else 10 ** 6
+    qi = 70
+    # just inside and just outside the window, just inside and just outside the kept first tokens, the far first token
+    plant = [(qi, max(qi - w + 1, 0)), (qi - 1, max(qi - 1 - w, 0)), (qi - 2, max(keep - 1, 0)), (qi - 3, keep), (qi - 4, 0)]
+    q, k, v = _planted(T, H, G, D, Dv, plant)
+    qd, kd, vd = q.to(dt), k.to(dt), v.to(dt)
+    ref = torch.stack([O.attention_one_head(qd[:, h].to(F64), kd[:, h // (H // G)].to(F64), vd[:, h // (H // G)].to(F64),
+                                            h, H, scale, size, keep) for h in range(H)], 1)
+    S = 96
+    ck, cv = torch.zeros(2, G, S, D, dtype=dt, device=dev), torch.zeros(2, G, S, Dv, dtype=dt, device=dev)
+    ck[1, :, :T], cv[1, :, :T] = kd.transpose(0, 1).to(dev), vd.transpose(0, 1).to(dev)
+    slopes = wa.distance_slopes(H, device=dev)
+    line = torch.tensor([1], device=dev)
+    out = wa.window_attention_prefill(qd.to(dev).unsqueeze(0), ck, cv, torch.tensor([0], device=dev), scale, size, keep,
+                                      slopes, seq_ids=line)
+    close(out[0], ref, dt, scale=25.0)
+    # a portion that starts in the middle reads the earlier keys from the cache
+    out2 = wa.window_attention_prefill(qd[41:].to(dev).unsqueeze(0), ck, cv, torch.tensor([41], device=dev), scale, size,
+                                       keep, slopes, seq_ids=line)
+    close(out2[0], ref[41:], dt, scale=25.0)
+    for p in (qi, qi - 1, qi - 2, qi - 3, qi - 4, 0, 1):
+        o = wa.window_attention_decode(qd[p].to(dev).unsqueeze(0), ck, cv, torch.tensor([p], device=dev), scale, size,
+                                       keep, slopes, seq_ids=line)
+        close(o[0], ref[p], dt, scale=25.0)
+
+
+@case
+def test_window_attention_paged_cache_and_padding(dev, dt):
+    torch.manual_seed(3)
+    B, T, H, G, D, Dv, ps, scale = 3, 37, 6, 3, 8, 12, 8, 0.3
+    n_new = [37, 2, 20]
+    pages = 24
+    table = torch.randperm(pages).reshape(3, 8).to(torch.int32)
+    ck, cv = torch.zeros(pages, G, ps, D, dtype=dt, device=dev), torch.zeros(pages, G, ps, Dv, dtype=dt, device=dev)
+    lines = torch.tensor([2, 0, 1])
+    qkv = torch.randn(B, T, H * D + G * (D + Dv)).to(dt)
+    kw = dict(block_table=table.to(dev), page_size=ps)
+    q = wa.qk_norm_cache_write(qkv.to(dev), ck, cv, torch.zeros(B, dtype=torch.int32, device=dev), H, G, D, Dv, 1e-5,
+                               n_new=torch.tensor(n_new, device=dev), seq_ids=lines.to(dev), **kw)
+    out = wa.window_attention_prefill(q, ck, cv, torch.zeros(B, dtype=torch.int32, device=dev), scale, 9, 2,
+                                      wa.distance_slopes(H, device=dev), n_new=torch.tensor(n_new, device=dev),
+                                      seq_ids=lines.to(dev), **kw)
+    x = qkv.to(F64)
+    for b in range(B):
+        n = n_new[b]
+        qq = O.unit_rms(x[b, :n, :H * D].reshape(n, H, D), 1e-5).to(dt).to(F64)
+        kk = O.unit_rms(x[b, :n, H * D:(H + G) * D].reshape(n, G, D), 1e-5).to(dt).to(F64)
+        vv = x[b, :n, (H + G) * D:].reshape(n, G, Dv)
+        close(out[b, :n], O.attention_vectorised(qq, kk, vv, H, G, scale, 9, 2), dt)
+        assert float(out[b, n:].abs().sum()) == 0.0
+
+
+@case
+@pytest.mark.parametrize("N,W,E,I,top,F,Fs", [(23, 48, 6, 1, 2, 32, 40), (4, 30, 2, 0, 1, 9, 0), (70, 64, 3, 3, 4, 16, 24)])
+def test_router_experts_and_combination(dev, dt, N, W, E, I, top, F, Fs):
+    torch.manual_seed(5)
+    cfg = mlp(router={"experts": E, "identity": I, "scale": 1.5, "top": top}, expert={"ff": F, "limit": 0.8},
+              shared={"ff": Fs, "limit": 0.6} if Fs else None)
+    sd = O.random_weights(config(layers=[{"type": "attention", "mixer": mixer(), "mlp": cfg}], width=W), seed=11)
+    # corrections large enough to change the choice without entering the weights
+    sd["l0.mlp.correction"] = (torch.randn(E + I) * 0.3).to(torch.bfloat16).float()
+    h = (torch.randn(N, W) * 1.5).to(dt)
+    from neuronx_distributed_llama3_2_b200.modules.moe import SparseMoE
+
+    m = SparseMoE(W, E, top, F, 0.8, num_identity_experts=I, affinity_scale=1.5, shared_intermediate_size=Fs,
+                  shared_limit=0.6, dtype=dt, device=torch.device(dev))
+    full = convert_gekazen_state_dict(sd, GekazenConfig.from_dict(
+        config(layers=[{"type": "attention", "mixer": mixer(), "mlp": cfg}], width=W), torch_dtype=dt))
+    m.load_state_dict({k[len("layers.0.mlp."):]: v for k, v in full.items() if k.startswith("layers.0.mlp.")})
+    ref = O.moe(h.to(F64), {k: v.to(F64) for k, v in sd.items()}, "l0.mlp.", cfg)
+    idx, wts, _ = m.router.select(h.to(dev))
+    for t in range(N):
+        s, chosen = O.route(h[t].to(F64), sd["l0.mlp.router"].to(F64), sd["l0.mlp.correction"].to(F64), top)
+        assert sorted(idx[t].tolist()) == sorted(chosen)
+        for e, wgt in zip(idx[t].tolist(), wts[t].tolist()):
+            assert abs(wgt - float(s[e]) * 1.5) < 1e-5
+    for path in ("pairs", "sorted"):
+        close(m(h.to(dev), path=path), ref, dt, scale=3.0)
+
+
+@case
+def test_post_norm_residual_keeps_an_fp32_stream(dev, dt):
+    torch.manual_seed(2)
+    x, y, w = torch.randn(7, 50) * 30, torch.randn(7, 50).to(dt), torch.randn(50) * 0.2
+    ref = x.to(F64) + O.zero_centred_norm(y.to(F64), w.to(F64), 1e-5)
+    xs, h = norm_ops.post_norm_residual_(x.clone().to(dev), y.to(dev), w.to(dev), 1e-5, dt)
+    assert xs.dtype == torch.float32 and h.dtype == dt
+    close(xs, ref, torch.float32, scale=0.1)             # the stream itself is fp32 whatever the activation dtype
+    assert torch.equal(h.cpu(), xs.cpu().to(dt))
+    close(norm_ops.rms_norm_offset(x.to(dev), w.to(dev), 1e-5, dt), O.zero_centred_norm(x.to(F64), w.to(F64), 1e-5), dt)
+
+
+# ---- the model through the framework -----------------------------------------------------------------------------------
+@case
+@pytest.mark.parametrize("cfg", [config(), ODD], ids=["mixed", "odd"])
+def test_prefill_matches_oracle_and_token_by_token_decoding(dev, dt, cfg):
+    toks = tokens_of(cfg, 45, 1)
+    model, sd = build(cfg, dev, dt)
+    ref = O.forward(cfg, sd, toks)
+    want = list(range(45))
+    whole = replay(model, [([{"id": "a", "tokens": toks, "want": want}], ["a"])])["a"]
+    check_rows(whole, ref, want, dt)
+    steps = [([{"id": "b", "tokens": toks[:1], "want": [0]}], [])]
+    steps += [([{"id": "b", "tokens": [t], "want": [0]}], []) for t in toks[1:]]
+    check_rows(replay(model, steps)["b"], ref, want, dt)
+
+
+@case
+@pytest.mark.parametrize("portion", [2, 5, 16])
+def test_portions_of_a_prompt(dev, dt, portion):
+    cfg = config()
+    toks = tokens_of(cfg, 41, 2)
+    model, sd = build(cfg, dev, dt)
+    ref = O.forward(cfg, sd, toks)
+    steps, places = [], []
+    for lo in range(0, 41, portion):
+        part = toks[lo:lo + portion]
+        steps.append(([{"id": "p", "tokens": part, "want": list(range(len(part)))}], []))
+        places += list(range(lo, lo + len(part)))
+    check_rows(replay(model, steps)["p"], ref, places, dt)
+
+
+@case
+def test_unequal_batch_equals_each_alone_and_lines_are_reused(dev, dt):
+    cfg = config()
+    model, sd = build(cfg, dev, dt, lines=3)
+    lens = {"a": 1, "b": 30, "c": 13, "d": 22, "e": 9}
+    toks = {k: tokens_of(cfg, n + 6, 10 + i) for i, (k, n) in enumerate(lens.items())}
+    ref = {k: O.forward(cfg, sd, v) for k, v in toks.items()}
+    first = [{"id": k, "tokens": toks[k][:lens[k]], "want": [lens[k] - 1]} for k in "abc"]
+    steps = [(first, ["a"])]                                     # a one-token request ends at once: its line is free
+    for s in range(3):
+        steps.append(([{"id": k, "tokens": [toks[k][lens[k] + s]], "want": [0]} for k in "bc"], ["c"] if s == 2 else []))
+    # two new requests take the lines that a and c gave back (stale keys of longer requests lie behind them)
+    steps.append(([{"id": k, "tokens": toks[k][:lens[k]], "want": [0, lens[k] - 1]} for k in "de"], []))
+    for s in range(6):
+        steps.append(([{"id": k, "tokens": [toks[k][lens[k] + s]], "want": [0]} for k in "de"], []))
+    got = replay(model, steps)
+    check_rows(got["a"], ref["a"], [0], dt)
+    for k in "bc":
+        check_rows(got[k], ref[k], [lens[k] - 1, lens[k], lens[k] + 1, lens[k] + 2], dt)
+    for k in "de":
+        check_rows(got[k], ref[k], [0, lens[k] - 1] + [lens[k] + s for s in range(6)], dt)
+
+
+@case
+def test_long_decoding_past_every_window(dev, dt):
+    cfg = config()
+    toks = tokens_of(cfg, 90, 4)
+    model, sd = build(cfg, dev, dt)
+    ref = O.forward(cfg, sd, toks)
+    steps = [([{"id": "x", "tokens": toks[:5], "want": [4]}], [])]
+    steps += [([{"id": "x", "tokens": [t], "want": [0]}], []) for t in toks[5:]]
+    check_rows(replay(model, steps)["x"], ref, list(range(4, 90)), dt)
+
+
+@case
+def test_a_far_key_decides_the_output(dev, dt):
+    """One layer, window 6 with 2 kept tokens: the value of token 1 (kept, far away) is made huge, so a run that drops
+    the kept tokens -- in the prompt or while decoding -- changes the logits completely."""
+    cfg = config(layers=[{"type": "attention", "mixer": mixer(mask={"size": 6, "keep_first": 2}), "mlp": None}])
+    sd = O.random_weights(cfg, seed=3)
+    sd["l0.mix.v.b"] = sd["l0.mix.v.b"] * 0
+    sd["embed"][5] = sd["embed"][5] * 8            # token id 5 sits at position 1 only
+    toks = [t if t != 5 else 6 for t in tokens_of(cfg, 60, 9)]
+    toks[1] = 5
+    model, _ = build(cfg, dev, dt, sd=sd)
+    ref = O.forward(cfg, sd, toks)
+    cut = dict(cfg, layers=[{"type": "attention", "mixer": mixer(mask={"size": 6, "keep_first": 1}), "mlp": None}])
+    assert float((O.forward(cut, sd, toks)[50] - ref[50]).abs().max()) > 0.05      # the oracle itself sees the difference
+    steps = [([{"id": "f", "tokens": toks[:40], "want": [7, 8, 39]}], [])]
+    steps += [([{"id": "f", "tokens": [t], "want": [0]}], []) for t in toks[40:]]
+    check_rows(replay(model, steps)["f"], ref, [7, 8, 39] + list(range(40, 60)), dt)
+
+
+@case
+def test_greedy_generation_through_generate_and_the_continuous_batcher(dev, dt):
+    cfg = config()
+    sd = O.random_weights(cfg, seed=5)
+    prompts = [tokens_of(cfg, n, 20 + n) for n in (7, 12, 3)]
+
+    def oracle_greedy(p, new):
+        seq = list(p)
+        for _ in range(new):
+            seq.append(int(O.forward(cfg, sd, seq)[-1].argmax()))
+        return seq[len(p):]
+
+    want = [oracle_greedy(p, 6) for p in prompts]
+    model, _ = build(cfg, dev, dt, lines=3, sd=sd)
+    T = max(len(p) for p in prompts)
+    ids = torch.zeros(3, T, dtype=torch.long)
+    mask = torch.zeros(3, T, dtype=torch.long)
+    for b, p in enumerate(prompts):
+        ids[b, :len(p)], mask[b, :len(p)] = torch.tensor(p), 1
+    out = model.generate(ids.to(dev), mask.to(dev), max_new_tokens=6)
+    margin_ok = dt == torch.float32
+    for b, p in enumerate(prompts):
+        got = out[b, len(p):len(p) + 6].tolist()
+        assert got == want[b] or not margin_ok, (got, want[b])
+        assert got[0] == want[b][0]
+    # continuous batching over a page pool smaller than lines * pages per line: pages are freed and handed out again
+    from neuronx_distributed_llama3_2_b200.inference.continuous_batching import ContinuousBatcher
+
+    model2, _ = build(cfg, dev, dt, lines=2, sd=sd, paged=True, pages=9, page_size=4, seq_len=32)
+    cb = ContinuousBatcher(model2)
+    rids = [cb.submit(torch.tensor(p), 6) for p in prompts]
+    res = cb.run()
+    for rid, w in zip(rids, want):
+        assert res[rid][:6] == w or not margin_ok, (res[rid], w)
+        assert res[rid][0] == w[0]
+
+
+def test_registry_and_command_line_replay(tmp_path):
+    """``bin/trace_run`` on a model directory: family chosen from config.json, steps on stdin, logits in files."""
+    from safetensors.torch import save_file
+
+    cfg = ODD
+    sd = O.random_weights(cfg, seed=8)
+    mdir = tmp_path / "model"
+    mdir.mkdir()
+    (mdir / "config.json").write_text(json.dumps(cfg))
+    save_file({k: v.to(torch.bfloat16).contiguous() for k, v in sd.items()}, str(mdir / "model.safetensors"))
+    toks = tokens_of(cfg, 20, 3)
+    steps = [{"step": 0, "entries": [{"id": "r", "tokens": toks[:15], "want": [0, 14]}], "end": []},
+             {"step": 1, "entries": [{"id": "r", "tokens": toks[15:16], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "r", "tokens": toks[16:17], "want": [0]}], "end": ["r"]}]
+    out = tmp_path / "out"
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", str(mdir), "--dtype", "float32",
+                        "--out", str(out), "--max-tokens", "64"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                       capture_output=True, text=True, env=env, timeout=300)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [ln for ln in p.stdout.split("\n") if ln.startswith("done")] == ["done 0", "done 1", "done 2"]
+    assert not (out / "1.f32").exists()
+    ref = O.forward(cfg, sd, toks)
+    import numpy as np
+
+    a = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").reshape(2, cfg["vocab"]))
+    b = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4").reshape(1, cfg["vocab"]))
+    check_rows([a[0], a[1], b[0]], ref, [0, 14, 16], torch.float32)

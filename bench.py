@@ -55,6 +55,10 @@ def parse_args():
     ap.add_argument("--no-inference", action="store_true",
                     help="skip the second half of the headline metric (Llama-3.2-1B TTFT / decode tokens/s, reported "
                          "under the extra key \"inference\")")
+    ap.add_argument("--families", action="store_true",
+                    help="instead of the headline workload: serving throughput (prefill and decode tokens/s) of the "
+                         "Gekazen family next to the Mixtral-style decoder at equal layer sizes, and their like-for-like "
+                         "kernels with roofline fractions (1 GPU; one JSON line)")
     ap.add_argument("--profile", default="", help="diagnosis only: write a kernel timeline summary of 2 steps (rank 0) "
                     "to this file instead of timing (numbers under a profiler are never bench values)")
     return ap.parse_args()
@@ -425,6 +429,16 @@ def main():
     from neuronx_distributed_llama3_2_b200.ops import _lib, backend
 
     assert _lib.available(), "kernel library must be loadable on the GPU box"
+    if args.families:
+        from neuronx_distributed_llama3_2_b200.inference import family_bench
+
+        assert world == 1, "--families is a single-GPU comparison"
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        out = family_bench.run(steps=args.steps, warmup=args.warmup, device=dev)
+        out["clocks"] = sampler.stop()
+        print(json.dumps(out))
+        return
     t_start = time.time()
     S = args.seq_len
     # --impl baseline: the library arm alone (cuBLAS + SDPA + NCCL with the same layers)

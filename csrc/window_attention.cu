@@ -4,7 +4,9 @@
 //   visible(i, j) = j <= i and (window <= 0 or i - j < window or j < keep_first)
 //   score(i, j)   = scale * <q_i, k_j> - slope_h * (i - j)            (slopes == NULL: no bias)
 //
-// Three kernels:
+// Kernels:
+//   window_attn_prefill_mma  bf16, head sizes from a compiled list: tensor-core prefill (see below); the generic prefill
+//                         kernel serves every other case (fp32, other sizes)
 //   qk_norm_cache_write   rows of the fused projection output -> unit-RMS q (written out) and unit-RMS k + v written
 //                         into the cache at (line, position); statistics in fp32
 //   window_attn_prefill   a tile of 16 queries of one head per CTA, keys and values streamed from the cache in tiles of
@@ -14,6 +16,7 @@
 //                         heads of the group, merged through shared memory
 // The cache is contiguous [lines, G, S, D] or paged [pages, G, page, D] with a block table [lines, cols].
 #include "common.cuh"
+#include "mma_sync.cuh"
 
 namespace {
 
@@ -210,6 +213,215 @@ window_attn_prefill_kernel(const T* __restrict__ q, const T* __restrict__ cache_
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
+// Tensor-core prefill for bf16 with compile-time head sizes (multiples of 16): 64 queries of one head per CTA (16 per
+// warp, mma.sync m16n8k16), key / value tiles of 64 cache rows double-buffered with cp.async, rows padded by 16 bytes
+// in shared memory (ldmatrix without bank conflicts for any D that is a multiple of 16), scores, bias, mask and the
+// online softmax in fp32 registers, P handed to the PV product as A fragments without leaving registers.  The key
+// tiles visited are the ones that hold kept first tokens plus the ones the window of some query of the tile reaches.
+constexpr int MQ = 64, MK = 64, M_THREADS = 128;
+
+template <int D, int DV>
+__global__ void __launch_bounds__(M_THREADS)
+window_attn_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache_k,
+                               const bf16* __restrict__ cache_v, CacheAddr ka, CacheAddr va, bf16* __restrict__ out,
+                               const int* __restrict__ q_start, const int* __restrict__ n_new,
+                               const int* __restrict__ seq_ids, const float* __restrict__ slopes, int Tn, int H, int G,
+                               float scale, int window, int keep_first) {
+    constexpr int LDK = D + 8, LDV = DV + 8, CK = D / 8, CV = DV / 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);       // [MQ][LDK]
+    bf16* Ks = Qs + MQ * LDK;                           // [2][MK][LDK]
+    bf16* Vs = Ks + 2 * MK * LDK;                       // [2][MK][LDV]
+    __shared__ long long koff[2][MK], voff[2][MK];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int q0 = blockIdx.x * MQ, h = blockIdx.y, b = blockIdx.z;
+    const int g = h / (H / G);
+    const int nb = n_new != nullptr ? min(n_new[b], Tn) : Tn;
+    if (q0 >= nb) {                                      // padding rows: zeros
+        for (int idx = tid; idx < MQ * (DV / 2); idx += M_THREADS) {
+            const int r = idx / (DV / 2), c = idx - r * (DV / 2);
+            if (q0 + r < Tn)
+                *reinterpret_cast<uint32_t*>(out + (((long long)b * Tn + q0 + r) * H + h) * DV + 2 * c) = 0u;
+        }
+        return;
+    }
+    const int start = q_start[b];
+    const int line = seq_ids != nullptr ? seq_ids[b] : b;
+    const int p_lo = start + q0;
+    const int p_hi = start + min(q0 + MQ, nb) - 1;
+    const int last_tile = p_hi / MK;
+    int t_win = 0, n_sink_tiles = 0;
+    if (window > 0) {
+        t_win = max(0, p_lo - window + 1) / MK;
+        n_sink_tiles = min((keep_first + MK - 1) / MK, t_win);
+    }
+    const int n_tiles = n_sink_tiles + last_tile - t_win + 1;
+
+    const uint32_t qs_addr = (uint32_t)__cvta_generic_to_shared(Qs);
+    const uint32_t ks_addr = (uint32_t)__cvta_generic_to_shared(Ks);
+    const uint32_t vs_addr = (uint32_t)__cvta_generic_to_shared(Vs);
+
+    for (int idx = tid; idx < MQ * CK; idx += M_THREADS) {
+        const int r = idx / CK, c = idx - r * CK;
+        const bool ok = q0 + r < nb;
+        const bf16* src = ok ? q + (((long long)b * Tn + q0 + r) * H + h) * D + c * 8 : q;
+        mma::cp_async16(qs_addr + (r * LDK + c * 8) * 2, src, ok);
+    }
+    auto issue = [&](int n, int buf) {
+        const int kt = n < n_sink_tiles ? n : t_win + (n - n_sink_tiles);
+        if (tid < MK) {
+            const int pos = kt * MK + tid;
+            koff[buf][tid] = pos <= p_hi ? ka.row(line, g, pos) : -1;
+        } else {
+            const int pos = kt * MK + tid - MK;
+            voff[buf][tid - MK] = pos <= p_hi ? va.row(line, g, pos) : -1;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < MK * CK; idx += M_THREADS) {
+            const int r = idx / CK, c = idx - r * CK;
+            const bool ok = koff[buf][r] >= 0;
+            mma::cp_async16(ks_addr + ((buf * MK + r) * LDK + c * 8) * 2, ok ? cache_k + koff[buf][r] + c * 8 : cache_k, ok);
+        }
+        for (int idx = tid; idx < MK * CV; idx += M_THREADS) {
+            const int r = idx / CV, c = idx - r * CV;
+            const bool ok = voff[buf][r] >= 0;
+            mma::cp_async16(vs_addr + ((buf * MK + r) * LDV + c * 8) * 2, ok ? cache_v + voff[buf][r] + c * 8 : cache_v, ok);
+        }
+        mma::cp_async_commit();
+    };
+    issue(0, 0);                                          // one group: the Q tile and the first K/V tile
+
+    constexpr float LOG2E = 1.4426950408889634f;
+    const float sc2 = scale * LOG2E;
+    const float sl2 = (slopes != nullptr ? slopes[h] : 0.f) * LOG2E;
+    const int r_lo = warp * 16 + (lane >> 2);             // this thread's rows: r_lo and r_lo + 8
+    const int pi0 = start + q0 + r_lo, pi1 = pi0 + 8;
+    const bool ok0 = q0 + r_lo < nb, ok1 = q0 + r_lo + 8 < nb;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    float o[DV / 8][4];
+#pragma unroll
+    for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    uint32_t qf[D / 16][4];
+
+    for (int n = 0; n < n_tiles; ++n) {
+        const int buf = n & 1;
+        if (n + 1 < n_tiles) {
+            issue(n + 1, buf ^ 1);
+            mma::cp_async_wait<1>();
+        } else {
+            mma::cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (n == 0) {
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk)
+                mma::ldsm_x4(qf[kk], qs_addr + ((warp * 16 + (lane & 15)) * LDK + kk * 16 + (lane >> 4) * 8) * 2);
+        }
+        const int kt = n < n_sink_tiles ? n : t_win + (n - n_sink_tiles);
+        const int k0 = kt * MK;
+        float s[MK / 8][4];
+#pragma unroll
+        for (int i = 0; i < MK / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+        const uint32_t kb_addr = ks_addr + buf * MK * LDK * 2;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+            for (int np = 0; np < MK / 16; ++np) {
+                uint32_t bfr[4];
+                const int row = np * 16 + (lane & 7) + (lane >> 4) * 8;
+                mma::ldsm_x4(bfr, kb_addr + (row * LDK + kk * 16 + ((lane >> 3) & 1) * 8) * 2);
+                mma::mma16816(s[2 * np], qf[kk], bfr[0], bfr[1]);
+                mma::mma16816(s[2 * np + 1], qf[kk], bfr[2], bfr[3]);
+            }
+        }
+        // scale, distance bias, mask; row maxima
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < MK / 8; ++i) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = k0 + i * 8 + (lane & 3) * 2 + (e & 1);
+                const int pi = (e & 2) ? pi1 : pi0;
+                const int dist = pi - j;
+                const bool vis = ((e & 2) ? ok1 : ok0) && dist >= 0 && (window <= 0 || dist < window || j < keep_first);
+                const float v = vis ? s[i][e] * sc2 - sl2 * (float)dist : -INFINITY;
+                s[i][e] = v;
+                if (e & 2) mx1 = fmaxf(mx1, v); else mx0 = fmaxf(mx0, v);
+            }
+        }
+        mx0 = mma::quad_max(mx0);
+        mx1 = mma::quad_max(mx1);
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float a0 = exp2f(m0 - ms0), a1 = exp2f(m1 - ms1);
+        m0 = mn0;
+        m1 = mn1;
+        float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < MK / 8; ++i) {
+            s[i][0] = exp2f(s[i][0] - ms0);
+            s[i][1] = exp2f(s[i][1] - ms0);
+            s[i][2] = exp2f(s[i][2] - ms1);
+            s[i][3] = exp2f(s[i][3] - ms1);
+            ps0 += s[i][0] + s[i][1];
+            ps1 += s[i][2] + s[i][3];
+        }
+        l0 = l0 * a0 + ps0;
+        l1 = l1 * a1 + ps1;
+#pragma unroll
+        for (int i = 0; i < DV / 8; ++i) {
+            o[i][0] *= a0;
+            o[i][1] *= a0;
+            o[i][2] *= a1;
+            o[i][3] *= a1;
+        }
+        const uint32_t vb_addr = vs_addr + buf * MK * LDV * 2;
+#pragma unroll
+        for (int kb = 0; kb < MK / 16; ++kb) {
+            uint32_t pa[4];
+            pa[0] = mma::pack2(s[2 * kb][0], s[2 * kb][1]);
+            pa[1] = mma::pack2(s[2 * kb][2], s[2 * kb][3]);
+            pa[2] = mma::pack2(s[2 * kb + 1][0], s[2 * kb + 1][1]);
+            pa[3] = mma::pack2(s[2 * kb + 1][2], s[2 * kb + 1][3]);
+#pragma unroll
+            for (int dj = 0; dj < DV / 16; ++dj) {
+                uint32_t bfr[4];
+                const int row = kb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                mma::ldsm_x4_t(bfr, vb_addr + (row * LDV + dj * 16 + (lane >> 4) * 8) * 2);
+                mma::mma16816(o[2 * dj], pa, bfr[0], bfr[1]);
+                mma::mma16816(o[2 * dj + 1], pa, bfr[2], bfr[3]);
+            }
+        }
+        __syncthreads();                                  // the buffer is free for the tile after next
+    }
+    l0 = mma::quad_sum(l0);
+    l1 = mma::quad_sum(l1);
+    const float i0 = (ok0 && l0 > 0.f) ? 1.f / l0 : 0.f, i1 = (ok1 && l1 > 0.f) ? 1.f / l1 : 0.f;
+    bf16* out0 = out + (((long long)b * Tn + q0 + r_lo) * H + h) * DV + (lane & 3) * 2;
+    bf16* out1 = out0 + (long long)8 * H * DV;
+#pragma unroll
+    for (int i = 0; i < DV / 8; ++i) {
+        if (q0 + r_lo < Tn) *reinterpret_cast<uint32_t*>(out0 + i * 8) = mma::pack2(o[i][0] * i0, o[i][1] * i0);
+        if (q0 + r_lo + 8 < Tn) *reinterpret_cast<uint32_t*>(out1 + i * 8) = mma::pack2(o[i][2] * i1, o[i][3] * i1);
+    }
+}
+
+template <int D, int DV>
+int launch_prefill_mma(const void* q, const void* ck, const void* cv, CacheAddr ka, CacheAddr va, void* out,
+                       const int* q_start, const int* n_new, const int* seq_ids, const float* slopes, int B, int Tn, int H,
+                       int G, float scale, int window, int keep_first, cudaStream_t st) {
+    const size_t smem = (size_t)(MQ * (D + 8) + 2 * MK * (D + 8) + 2 * MK * (DV + 8)) * sizeof(bf16);
+    auto kern = window_attn_prefill_mma_kernel<D, DV>;
+    if (smem > 48 * 1024) NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid((Tn + MQ - 1) / MQ, H, B);
+    kern<<<grid, M_THREADS, smem, st>>>((const bf16*)q, (const bf16*)ck, (const bf16*)cv, ka, va, (bf16*)out, q_start,
+                                        n_new, seq_ids, slopes, Tn, H, G, scale, window, keep_first);
+    NXD_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
 constexpr int DEC_WARPS = 8, DEC_R = 8, DEC_MV = 8;   // query heads per CTA, value columns per lane (Dv <= 256)
 
 template <typename T>
@@ -389,17 +601,35 @@ NXD_API int nxd_qk_norm_cache_write(int dtype, const void* qkv, long long ld, vo
 
 // q [B, Tn, H, D] -> out [B, Tn, H, Dv]; the keys and values of positions [0, q_start[b] + n_new[b]) are read from the
 // cache (the new tokens' rows must have been written before).  slopes [H] fp32 or NULL; window <= 0: plain causal.
+// impl: 0 = choose, 1 = the generic kernel, 2 = the tensor-core kernel (an error when it does not apply).
 NXD_API int nxd_window_attn_prefill(int dtype, const void* q, const void* cache_k, const void* cache_v,
                                     long long k_stride_line, long long k_stride_head, long long v_stride_line,
                                     long long v_stride_head, const int* block_table, int page_size, int table_cols,
                                     void* out, const int* q_start, const int* n_new, const int* seq_ids,
                                     const float* slopes, int B, int Tn, int H, int G, int D, int Dv, float scale,
-                                    int window, int keep_first, void* stream) {
+                                    int window, int keep_first, int impl, void* stream) {
     NXD_REQUIRE(G > 0 && H % G == 0, "window attention: %d query heads over %d key/value heads", H, G);
     NXD_REQUIRE(Dv <= MAXC * 8, "window attention: value size %d above %d", Dv, MAXC * 8);
     if (B * Tn == 0) return 0;
     const CacheAddr ka = make_addr(k_stride_line, k_stride_head, block_table, page_size, table_cols, D);
     const CacheAddr va = make_addr(v_stride_line, v_stride_head, block_table, page_size, table_cols, Dv);
+    // bf16 with head sizes the tensor-core kernel is compiled for (cache rows must start on 16-byte boundaries, which a
+    // cache tensor with a row size that is a multiple of 8 guarantees); everything else takes the generic kernel
+    if (dtype == 0 && impl != 1 && Tn >= 16 && (k_stride_head % 8) == 0 && (v_stride_head % 8) == 0 &&
+        (k_stride_line % 8) == 0 && (v_stride_line % 8) == 0) {
+#define NXD_WA_CASE(DD, DDV)                                                                                          \
+    if (D == DD && Dv == DDV)                                                                                         \
+        return launch_prefill_mma<DD, DDV>(q, cache_k, cache_v, ka, va, out, q_start, n_new, seq_ids, slopes, B, Tn, H, \
+                                           G, scale, window, keep_first, (cudaStream_t)stream)
+        NXD_WA_CASE(32, 32);
+        NXD_WA_CASE(64, 64);
+        NXD_WA_CASE(96, 96);
+        NXD_WA_CASE(128, 128);
+        NXD_WA_CASE(64, 128);
+        NXD_WA_CASE(128, 64);
+#undef NXD_WA_CASE
+    }
+    NXD_REQUIRE(impl != 2, "window attention: no tensor-core kernel for bf16=%d D=%d Dv=%d", dtype == 0, D, Dv);
     if (dtype == 0)
         return launch_prefill<bf16>(q, cache_k, cache_v, ka, va, out, q_start, n_new, seq_ids, slopes, B, Tn, H, G, D, Dv,
                                     scale, window, keep_first, (cudaStream_t)stream);

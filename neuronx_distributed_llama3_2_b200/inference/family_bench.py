@@ -1,0 +1,204 @@
+"""Serving throughput of the Gekazen family next to the closest existing family (the Mixtral-style MoE decoder) at equal
+layer sizes, plus the like-for-like kernels of the two in isolation with their roofline fractions.
+
+Random-init bf16 weights, synthetic token ids.  Every number is CUDA-event time on the launching stream after >= 3
+warm-up runs, with a write through a buffer larger than L2 between timed runs; peaks come from ``MEASURED_PEAKS.json``
+(measured copy bandwidth and cuBLAS bf16 throughput) when the file is present.
+"""
+from __future__ import annotations
+
+import ctypes
+import json
+import os
+import statistics
+from typing import Callable, Dict, List
+
+import torch
+
+from ..models.gekazen import GekazenConfig
+from ..models.mixtral import MixtralConfig
+from ..ops import _lib
+from ..ops import attention as attn_ops
+from ..ops import moe_sparse  # noqa: F401
+from ..ops import norm as norm_ops
+from ..ops import window_attention as wa
+from .config import InferenceConfig
+from .model import GekazenInferenceModel, MixtralInferenceModel
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+SIZES = [
+    dict(name="w2048-d128", width=2048, layers=4, heads=16, kv_heads=4, dim=128, experts=8, top=2, ff=2048, window=1024,
+         keep_first=4, prefill_batch=4, prompt=2048, decode_batch=16),
+    dict(name="w4096-d128", width=4096, layers=2, heads=32, kv_heads=8, dim=128, experts=8, top=2, ff=4096, window=2048,
+         keep_first=4, prefill_batch=2, prompt=4096, decode_batch=32),
+    dict(name="w1024-d64", width=1024, layers=4, heads=16, kv_heads=16, dim=64, experts=16, top=4, ff=512, window=512,
+         keep_first=2, prefill_batch=8, prompt=1024, decode_batch=64),
+]
+VOCAB = 8192
+
+
+def peaks() -> Dict[str, float]:
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+    except (OSError, KeyError, ValueError):
+        return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class _Timer:
+    def __init__(self, device):
+        self.flush = torch.empty(192 << 20, dtype=torch.uint8, device=device)      # > 126 MB of L2
+
+    def __call__(self, fn: Callable[[], None], steps: int, warmup: int) -> float:
+        """Median milliseconds of ``fn`` over ``steps`` runs."""
+        for _ in range(max(warmup, 3)):
+            fn()
+        times = []
+        for _ in range(steps):
+            _lib.lib().nxd_l2_flush(_lib.ptr(self.flush), ctypes.c_size_t(self.flush.numel()), _lib.stream_ptr())
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+        return statistics.median(times)
+
+
+def gekazen_config(s: dict) -> GekazenConfig:
+    layer = {"type": "attention",
+             "mixer": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"],
+                       "scale": s["dim"] ** -0.5, "mask": {"size": s["window"], "keep_first": s["keep_first"]}},
+             "mlp": {"kind": "moe", "expert": {"ff": s["ff"], "limit": 7.0},
+                     "router": {"experts": s["experts"], "identity": 0, "scale": 1.0, "top": s["top"]}, "shared": None}}
+    return GekazenConfig.from_dict({"architecture": "Gekazen", "vocab": VOCAB, "width": s["width"], "norm": {"eps": 1e-5},
+                                    "layers": [layer] * s["layers"]}, torch_dtype=torch.bfloat16)
+
+
+def mixtral_config(s: dict) -> MixtralConfig:
+    return MixtralConfig(vocab_size=VOCAB, hidden_size=s["width"], intermediate_size=s["ff"],
+                         num_hidden_layers=s["layers"], num_attention_heads=s["heads"],
+                         num_key_value_heads=s["kv_heads"], head_dim=s["dim"], rope_scaling=None,
+                         max_position_embeddings=s["prompt"] + 64, tie_word_embeddings=False,
+                         num_local_experts=s["experts"], num_experts_per_tok=s["top"], capacity_factor=None,
+                         sequence_parallel_enabled=False, torch_dtype=torch.bfloat16)
+
+
+def _serve(model, s: dict, timer: _Timer, steps: int, warmup: int, dev) -> Dict[str, float]:
+    Bp, T, Bd = s["prefill_batch"], s["prompt"], s["decode_batch"]
+    ids = torch.randint(1, VOCAB, (Bp, T), device=dev)
+    pos = torch.arange(T, device=dev).unsqueeze(0).expand(Bp, T).contiguous()
+    lines = torch.arange(Bp, dtype=torch.int32, device=dev)
+    last = torch.full((Bp,), T - 1, device=dev)
+    pre = timer(lambda: model.forward_infer(ids, pos, seq_ids=lines, last_token_index=last), steps, warmup)
+    # every decode line holds T tokens of context: fill the lines Bp at a time, then step at position T
+    for lo in range(0, Bd, Bp):
+        n = min(Bp, Bd - lo)
+        model.forward_infer(ids[:n], pos[:n], seq_ids=torch.arange(lo, lo + n, dtype=torch.int32, device=dev),
+                            last_token_index=last[:n])
+    tok = torch.randint(1, VOCAB, (Bd, 1), device=dev)
+    dpos = torch.full((Bd, 1), T, device=dev)
+    dl = torch.arange(Bd, dtype=torch.int32, device=dev)
+    dec = timer(lambda: model.forward_infer(tok, dpos, seq_ids=dl), steps, warmup)
+    return {"prefill_ms": pre, "prefill_tokens_per_s": Bp * T / pre * 1e3, "decode_ms": dec,
+            "decode_tokens_per_s": Bd / dec * 1e3}
+
+
+def serve_case(s: dict, steps: int, warmup: int, dev) -> dict:
+    timer = _Timer(dev)
+    out = {"size": {k: v for k, v in s.items()}}
+    ic = dict(batch_size=s["decode_batch"], max_batch_size=s["decode_batch"], max_context_length=s["prompt"],
+              seq_len=s["prompt"] + 64, is_continuous_batching=True, use_cuda_graphs=False)
+    for name, make in (("gekazen", lambda: GekazenInferenceModel(gekazen_config(s), InferenceConfig(**ic), device=dev)),
+                       ("mixtral", lambda: MixtralInferenceModel(mixtral_config(s), InferenceConfig(**ic), device=dev))):
+        torch.manual_seed(0)
+        model = make()
+        model.init_kv_cache(device=dev)
+        out[name] = _serve(model, s, timer, steps, warmup, dev)
+        del model
+        torch.cuda.empty_cache()
+    out["gekazen_over_mixtral"] = {k: out["gekazen"][k] / out["mixtral"][k]
+                                   for k in ("prefill_tokens_per_s", "decode_tokens_per_s")}
+    return out
+
+
+def kernel_cases(s: dict, steps: int, warmup: int, dev) -> List[dict]:
+    """The attention and norm kernels of both families on the shapes of ``s``, alone, with roofline fractions."""
+    pk = peaks()
+    timer = _Timer(dev)
+    B, T, H, G, D = s["prefill_batch"], s["prompt"], s["heads"], s["kv_heads"], s["dim"]
+    W, win, keep, Bd = s["width"], s["window"], s["keep_first"], s["decode_batch"]
+    bf = torch.bfloat16
+    rows = []
+
+    def row(kernel, like, ms, flops=None, nbytes=None):
+        r = {"kernel": kernel, "like": like, "ms": ms}
+        if flops is not None:
+            r["tflops"] = flops / ms / 1e9
+            r["of_peak"] = r["tflops"] / pk["bf16_tflops"]
+        if nbytes is not None:
+            r["gbs"] = nbytes / ms / 1e6
+            r["of_peak"] = r["gbs"] / pk["hbm_gbs"]
+        r["peak"] = pk["source"]
+        rows.append(r)
+
+    # prefill attention: visible (query, key) pairs only are counted as work
+    q = torch.randn(B, T, H, D, device=dev, dtype=bf)
+    ck = torch.randn(max(B, Bd), G, T + 64, D, device=dev, dtype=bf)
+    cv = torch.randn(max(B, Bd), G, T + 64, D, device=dev, dtype=bf)
+    zero = torch.zeros(B, dtype=torch.int32, device=dev)
+    slopes = wa.distance_slopes(H, device=dev)
+    i = torch.arange(T).reshape(T, 1)
+    j = torch.arange(T).reshape(1, T)
+    pairs_win = int(((j <= i) & ((i - j < win) | (j < keep))).sum())
+    pairs_causal = T * (T + 1) // 2
+    ms = timer(lambda: wa.window_attention_prefill(q, ck, cv, zero, D ** -0.5, win, keep, slopes), steps, warmup)
+    row("window_attn_prefill_mma (window, kept tokens, bias)", "prefill attention", ms, flops=4.0 * D * pairs_win * H * B)
+    ms = timer(lambda: wa.window_attention_prefill(q, ck, cv, zero, D ** -0.5, None, 0, slopes), steps, warmup)
+    row("window_attn_prefill_mma (plain causal, bias)", "prefill attention", ms, flops=4.0 * D * pairs_causal * H * B)
+    qh = q.permute(0, 2, 1, 3)
+    kh, vh = ck[:B, :, :T], cv[:B, :, :T]
+    ms = timer(lambda: attn_ops.flash_attn_func(qh, kh, vh, causal=True), steps, warmup)
+    row("flash attention forward (tcgen05, plain causal)", "prefill attention", ms, flops=4.0 * D * pairs_causal * H * B)
+    # decode attention: bytes of the cache rows that have to be read
+    qd = torch.randn(Bd, H, D, device=dev, dtype=bf)
+    posd = torch.full((Bd,), T, dtype=torch.int32, device=dev)
+    seen = min(T + 1, win) + min(keep, max(T + 1 - win, 0))
+    ms = timer(lambda: wa.window_attention_decode(qd, ck, cv, posd, D ** -0.5, win, keep, slopes), steps, warmup)
+    row("window_attn_decode", "decode attention", ms, nbytes=2.0 * seen * G * 2 * D * Bd)
+    lens = torch.full((Bd,), T + 1, dtype=torch.int32, device=dev)
+    ms = timer(lambda: attn_ops.decode_attention(qd, ck, cv, lens), steps, warmup)
+    row("decode attention (full context)", "decode attention", ms, nbytes=2.0 * (T + 1) * G * 2 * D * Bd)
+    # norms on the prefill activations
+    N = B * T
+    x32 = torch.randn(N, W, device=dev)
+    y = torch.randn(N, W, device=dev, dtype=bf)
+    w32 = torch.zeros(W, device=dev)
+    ms = timer(lambda: norm_ops.post_norm_residual_(x32, y, w32, 1e-5, bf), steps, warmup)
+    row("post-norm + fp32 residual (+ bf16 copy)", "norm", ms, nbytes=float(N * W * (2 + 4 + 4 + 2)))
+    xb, rb, wb = y, torch.randn(N, W, device=dev, dtype=bf), torch.ones(W, device=dev, dtype=bf)
+    ms = timer(lambda: norm_ops.fused_add_rms_norm(xb, rb, wb, 1e-5), steps, warmup)
+    row("fused add + RMSNorm (bf16 residual)", "norm", ms, nbytes=float(N * W * 2 * 4))
+    # q/k normalisation + cache write against rotation + cache write
+    n_out = (H + 2 * G) * D
+    qkv = torch.randn(B, T, n_out, device=dev, dtype=bf)
+    ms = timer(lambda: wa.qk_norm_cache_write(qkv, ck, cv, zero, H, G, D, D, 1e-5), steps, warmup)
+    row("unit-RMS q/k + cache write", "projection epilogue", ms, nbytes=float(2 * N * n_out * 2))
+    return rows
+
+
+def run(steps: int = 10, warmup: int = 3, device=None, sizes=None) -> dict:
+    dev = device or torch.device("cuda", torch.cuda.current_device())
+    before = _lib.kernel_launches()
+    out = {"metric": "Gekazen vs Mixtral-style decoder, serving throughput at equal layer sizes", "dtype": "bf16",
+           "data": "synthetic token ids, random-init weights", "steps": steps, "warmup": max(warmup, 3),
+           "l2": "192 MB written between timed runs", "peaks": peaks(), "cases": [], "kernels": {}}
+    for s in (sizes or SIZES):
+        out["cases"].append(serve_case(s, steps, warmup, dev))
+        out["kernels"][s["name"]] = kernel_cases(s, steps, warmup, dev)
+    out["gpu_launches"] = _lib.kernel_launches() - before
+    return out

@@ -138,8 +138,11 @@ def window_attention_prefill(q: torch.Tensor, cache_k: torch.Tensor, cache_v: to
                              scale: float, window: Optional[int] = None, keep_first: int = 0,
                              slopes: Optional[torch.Tensor] = None, n_new: Optional[torch.Tensor] = None,
                              seq_ids: Optional[torch.Tensor] = None, block_table: Optional[torch.Tensor] = None,
-                             page_size: int = 0) -> torch.Tensor:
-    """``q [B, T, H, D]``: new tokens of every row at positions ``q_start[b] + t`` (their keys / values already in the
+                             page_size: int = 0, impl: str = "auto") -> torch.Tensor:
+    """``impl``: ``auto`` | ``generic`` (fp32-math tile kernel, any sizes) | ``mma`` (bf16 tensor-core kernel, an error
+    where it does not apply) -- for tests and measurements.
+
+    ``q [B, T, H, D]``: new tokens of every row at positions ``q_start[b] + t`` (their keys / values already in the
     cache) -> ``[B, T, H, Dv]``.  Rows ``t >= n_new[b]`` are padding and come out as zeros."""
     B, T, H, D = q.shape
     G, Dv = cache_k.shape[1], cache_v.shape[3]
@@ -154,7 +157,7 @@ def window_attention_prefill(q: torch.Tensor, cache_k: torch.Tensor, cache_v: to
                                        *cargs, _lib.ptr(out), _lib.ptr(qs), _lib.ptr(nn_), _lib.ptr(sid),
                                        _lib.ptr(slopes), _c.c_int(B), _c.c_int(T), _c.c_int(H), _c.c_int(G), _c.c_int(D),
                                        _c.c_int(Dv), _c.c_float(scale), _c.c_int(w), _c.c_int(keep_first),
-                                       _lib.stream_ptr())
+                                       _c.c_int({"auto": 0, "generic": 1, "mma": 2}[impl]), _lib.stream_ptr())
         _lib.check(rc, "nxd_window_attn_prefill", L)
         return out
     out = torch.zeros(B, T, H, Dv, dtype=q.dtype, device=q.device)

@@ -213,12 +213,12 @@ window_attn_prefill_kernel(const T* __restrict__ q, const T* __restrict__ cache_
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// Tensor-core prefill for bf16 with compile-time head sizes (multiples of 16): 64 queries of one head per CTA (16 per
+// Tensor-core prefill for bf16 with compile-time head sizes (multiples of 16): 128 queries of one head per CTA (16 per
 // warp, mma.sync m16n8k16), key / value tiles of 64 cache rows double-buffered with cp.async, rows padded by 16 bytes
 // in shared memory (ldmatrix without bank conflicts for any D that is a multiple of 16), scores, bias, mask and the
 // online softmax in fp32 registers, P handed to the PV product as A fragments without leaving registers.  The key
 // tiles visited are the ones that hold kept first tokens plus the ones the window of some query of the tile reaches.
-constexpr int MQ = 64, MK = 64, M_THREADS = 128;
+constexpr int MQ = 128, MK = 64, M_THREADS = 256;
 
 template <int D, int DV>
 __global__ void __launch_bounds__(M_THREADS)
@@ -273,7 +273,7 @@ window_attn_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restric
         if (tid < MK) {
             const int pos = kt * MK + tid;
             koff[buf][tid] = pos <= p_hi ? ka.row(line, g, pos) : -1;
-        } else {
+        } else if (tid < 2 * MK) {
             const int pos = kt * MK + tid - MK;
             voff[buf][tid - MK] = pos <= p_hi ? va.row(line, g, pos) : -1;
         }
@@ -335,19 +335,36 @@ window_attn_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restric
                 mma::mma16816(s[2 * np + 1], qf[kk], bfr[2], bfr[3]);
             }
         }
-        // scale, distance bias, mask; row maxima
+        // scale, distance bias, mask; row maxima.  A tile that every query of the CTA sees completely needs no mask.
         float mx0 = -INFINITY, mx1 = -INFINITY;
+        const bool full = q0 + MQ <= nb && k0 + MK - 1 <= p_lo &&
+                          (window <= 0 || p_hi - k0 < window || k0 + MK <= keep_first);
+        if (full) {
+            const float jb = (float)(k0 + (lane & 3) * 2);
+            const float c0 = sl2 * (jb - (float)pi0), c1 = sl2 * (jb - (float)pi1);     // -slope * (i - j) at column 0
 #pragma unroll
-        for (int i = 0; i < MK / 8; ++i) {
+            for (int i = 0; i < MK / 8; ++i) {
+                const float d = sl2 * (float)(i * 8);
+                s[i][0] = fmaf(s[i][0], sc2, c0 + d);
+                s[i][1] = fmaf(s[i][1], sc2, c0 + d + sl2);
+                s[i][2] = fmaf(s[i][2], sc2, c1 + d);
+                s[i][3] = fmaf(s[i][3], sc2, c1 + d + sl2);
+                mx0 = fmaxf(mx0, fmaxf(s[i][0], s[i][1]));
+                mx1 = fmaxf(mx1, fmaxf(s[i][2], s[i][3]));
+            }
+        } else {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int j = k0 + i * 8 + (lane & 3) * 2 + (e & 1);
-                const int pi = (e & 2) ? pi1 : pi0;
-                const int dist = pi - j;
-                const bool vis = ((e & 2) ? ok1 : ok0) && dist >= 0 && (window <= 0 || dist < window || j < keep_first);
-                const float v = vis ? s[i][e] * sc2 - sl2 * (float)dist : -INFINITY;
-                s[i][e] = v;
-                if (e & 2) mx1 = fmaxf(mx1, v); else mx0 = fmaxf(mx0, v);
+            for (int i = 0; i < MK / 8; ++i) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = k0 + i * 8 + (lane & 3) * 2 + (e & 1);
+                    const int pi = (e & 2) ? pi1 : pi0;
+                    const int dist = pi - j;
+                    const bool vis = ((e & 2) ? ok1 : ok0) && dist >= 0 && (window <= 0 || dist < window || j < keep_first);
+                    const float v = vis ? s[i][e] * sc2 - sl2 * (float)dist : -INFINITY;
+                    s[i][e] = v;
+                    if (e & 2) mx1 = fmaxf(mx1, v); else mx0 = fmaxf(mx0, v);
+                }
             }
         }
         mx0 = mma::quad_max(mx0);
@@ -528,6 +545,226 @@ window_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ cache_k
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Tensor-core decode for bf16: the (up to 16) query heads that share one key/value head are the 16 rows of the
+// mma.sync tiles, so a cache row is read once for the whole group.  One CTA per (row, key/value head): the visible
+// cache rows (kept first tokens, then the window) stream through the same double-buffered 64-row tiles as in prefill;
+// each of the four warps takes 16 rows of a tile and keeps its own online-softmax state, merged through shared memory.
+constexpr int DM_THREADS = 128, DM_ROWS = 16;
+
+template <int D, int DV>
+__global__ void __launch_bounds__(DM_THREADS)
+window_attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache_k,
+                              const bf16* __restrict__ cache_v, CacheAddr ka, CacheAddr va, bf16* __restrict__ out,
+                              const int* __restrict__ positions, const int* __restrict__ seq_ids,
+                              const float* __restrict__ slopes, int H, int G, float scale, int window, int keep_first,
+                              int groups_per_kv) {
+    constexpr int LDK = D + 8, LDV = DV + 8, CK = D / 8, CV = DV / 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);       // [DM_ROWS][LDK]
+    bf16* Ks = Qs + DM_ROWS * LDK;                      // [2][MK][LDK]
+    bf16* Vs = Ks + 2 * MK * LDK;                       // [2][MK][LDV]
+    __shared__ long long koff[2][MK], voff[2][MK];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int R_all = H / G;
+    const int g = blockIdx.x / groups_per_kv, r_base = (blockIdx.x % groups_per_kv) * DM_ROWS;
+    const int b = blockIdx.y;
+    const int R = min(DM_ROWS, R_all - r_base);
+    const int h0 = g * R_all + r_base;
+    const int p = positions[b];
+    const int line = seq_ids != nullptr ? seq_ids[b] : b;
+    const int last_tile = p / MK;
+    int t_win = 0, n_sink_tiles = 0;
+    if (window > 0) {
+        t_win = max(0, p - window + 1) / MK;
+        n_sink_tiles = min((keep_first + MK - 1) / MK, t_win);
+    }
+    const int n_tiles = n_sink_tiles + last_tile - t_win + 1;
+    const uint32_t qs_addr = (uint32_t)__cvta_generic_to_shared(Qs);
+    const uint32_t ks_addr = (uint32_t)__cvta_generic_to_shared(Ks);
+    const uint32_t vs_addr = (uint32_t)__cvta_generic_to_shared(Vs);
+
+    for (int idx = tid; idx < DM_ROWS * CK; idx += DM_THREADS) {
+        const int r = idx / CK, c = idx - r * CK;
+        const bool ok = r < R;
+        mma::cp_async16(qs_addr + (r * LDK + c * 8) * 2, ok ? q + ((long long)b * H + h0 + r) * D + c * 8 : q, ok);
+    }
+    auto issue = [&](int n, int buf) {
+        const int kt = n < n_sink_tiles ? n : t_win + (n - n_sink_tiles);
+        if (tid < MK) {
+            const int pos = kt * MK + tid;
+            koff[buf][tid] = pos <= p ? ka.row(line, g, pos) : -1;
+        } else {
+            const int pos = kt * MK + tid - MK;
+            voff[buf][tid - MK] = pos <= p ? va.row(line, g, pos) : -1;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < MK * CK; idx += DM_THREADS) {
+            const int r = idx / CK, c = idx - r * CK;
+            const bool ok = koff[buf][r] >= 0;
+            mma::cp_async16(ks_addr + ((buf * MK + r) * LDK + c * 8) * 2, ok ? cache_k + koff[buf][r] + c * 8 : cache_k, ok);
+        }
+        for (int idx = tid; idx < MK * CV; idx += DM_THREADS) {
+            const int r = idx / CV, c = idx - r * CV;
+            const bool ok = voff[buf][r] >= 0;
+            mma::cp_async16(vs_addr + ((buf * MK + r) * LDV + c * 8) * 2, ok ? cache_v + voff[buf][r] + c * 8 : cache_v, ok);
+        }
+        mma::cp_async_commit();
+    };
+    issue(0, 0);
+
+    constexpr float LOG2E = 1.4426950408889634f;
+    const float sc2 = scale * LOG2E;
+    const int r_lo = lane >> 2;                           // this thread's rows (query heads): r_lo and r_lo + 8
+    const bool ok0 = r_lo < R, ok1 = r_lo + 8 < R;
+    const float sl0 = (slopes != nullptr && ok0 ? slopes[h0 + r_lo] : 0.f) * LOG2E;
+    const float sl1 = (slopes != nullptr && ok1 ? slopes[h0 + r_lo + 8] : 0.f) * LOG2E;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    float o[DV / 8][4];
+#pragma unroll
+    for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    uint32_t qf[D / 16][4];
+
+    for (int n = 0; n < n_tiles; ++n) {
+        const int buf = n & 1;
+        if (n + 1 < n_tiles) {
+            issue(n + 1, buf ^ 1);
+            mma::cp_async_wait<1>();
+        } else {
+            mma::cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (n == 0) {
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk)
+                mma::ldsm_x4(qf[kk], qs_addr + ((lane & 15) * LDK + kk * 16 + (lane >> 4) * 8) * 2);
+        }
+        const int kt = n < n_sink_tiles ? n : t_win + (n - n_sink_tiles);
+        const int k0 = kt * MK + warp * 16;               // this warp's 16 cache rows of the tile
+        float s[2][4];
+        s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+        const uint32_t kb_addr = ks_addr + buf * MK * LDK * 2;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+            uint32_t bfr[4];
+            const int row = warp * 16 + (lane & 7) + (lane >> 4) * 8;
+            mma::ldsm_x4(bfr, kb_addr + (row * LDK + kk * 16 + ((lane >> 3) & 1) * 8) * 2);
+            mma::mma16816(s[0], qf[kk], bfr[0], bfr[1]);
+            mma::mma16816(s[1], qf[kk], bfr[2], bfr[3]);
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = k0 + i * 8 + (lane & 3) * 2 + (e & 1);
+                const int dist = p - j;
+                const bool vis = ((e & 2) ? ok1 : ok0) && dist >= 0 && (window <= 0 || dist < window || j < keep_first);
+                const float v = vis ? s[i][e] * sc2 - ((e & 2) ? sl1 : sl0) * (float)dist : -INFINITY;
+                s[i][e] = v;
+                if (e & 2) mx1 = fmaxf(mx1, v); else mx0 = fmaxf(mx0, v);
+            }
+        }
+        mx0 = mma::quad_max(mx0);
+        mx1 = mma::quad_max(mx1);
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float a0 = exp2f(m0 - ms0), a1 = exp2f(m1 - ms1);
+        m0 = mn0;
+        m1 = mn1;
+        float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            s[i][0] = exp2f(s[i][0] - ms0);
+            s[i][1] = exp2f(s[i][1] - ms0);
+            s[i][2] = exp2f(s[i][2] - ms1);
+            s[i][3] = exp2f(s[i][3] - ms1);
+            ps0 += s[i][0] + s[i][1];
+            ps1 += s[i][2] + s[i][3];
+        }
+        l0 = l0 * a0 + ps0;
+        l1 = l1 * a1 + ps1;
+        uint32_t pa[4];
+        pa[0] = mma::pack2(s[0][0], s[0][1]);
+        pa[1] = mma::pack2(s[0][2], s[0][3]);
+        pa[2] = mma::pack2(s[1][0], s[1][1]);
+        pa[3] = mma::pack2(s[1][2], s[1][3]);
+        const uint32_t vb_addr = vs_addr + buf * MK * LDV * 2;
+#pragma unroll
+        for (int dj = 0; dj < DV / 16; ++dj) {
+            uint32_t bfr[4];
+            const int row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+            mma::ldsm_x4_t(bfr, vb_addr + (row * LDV + dj * 16 + (lane >> 4) * 8) * 2);
+            o[2 * dj][0] *= a0;
+            o[2 * dj][1] *= a0;
+            o[2 * dj][2] *= a1;
+            o[2 * dj][3] *= a1;
+            o[2 * dj + 1][0] *= a0;
+            o[2 * dj + 1][1] *= a0;
+            o[2 * dj + 1][2] *= a1;
+            o[2 * dj + 1][3] *= a1;
+            mma::mma16816(o[2 * dj], pa, bfr[0], bfr[1]);
+            mma::mma16816(o[2 * dj + 1], pa, bfr[2], bfr[3]);
+        }
+        __syncthreads();
+    }
+    // merge the four warps: [warp][row][DV + 2] floats over the (now idle) tile buffers
+    l0 = mma::quad_sum(l0);
+    l1 = mma::quad_sum(l1);
+    float* Ms = reinterpret_cast<float*>(smem_raw);
+    constexpr int MS = DV + 2;
+    {
+        float* d0 = Ms + ((warp * DM_ROWS) + r_lo) * MS;
+        float* d1 = d0 + 8 * MS;
+#pragma unroll
+        for (int i = 0; i < DV / 8; ++i) {
+            const int c = i * 8 + (lane & 3) * 2;
+            d0[c] = o[i][0];
+            d0[c + 1] = o[i][1];
+            d1[c] = o[i][2];
+            d1[c + 1] = o[i][3];
+        }
+        if ((lane & 3) == 0) {
+            d0[DV] = m0;
+            d0[DV + 1] = l0;
+            d1[DV] = m1;
+            d1[DV + 1] = l1;
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < R * DV; idx += DM_THREADS) {
+        const int r = idx / DV, c = idx - r * DV;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mx = fmaxf(mx, Ms[(w * DM_ROWS + r) * MS + DV]);
+        float num = 0.f, den = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float* src = Ms + (w * DM_ROWS + r) * MS;
+            const float f = src[DV] == -INFINITY ? 0.f : exp2f(src[DV] - mx);
+            num = fmaf(f, src[c], num);
+            den = fmaf(f, src[DV + 1], den);
+        }
+        out[((long long)b * H + h0 + r) * DV + c] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    }
+}
+
+template <int D, int DV>
+int launch_decode_mma(const void* q, const void* ck, const void* cv, CacheAddr ka, CacheAddr va, void* out,
+                      const int* positions, const int* seq_ids, const float* slopes, int B, int H, int G, float scale,
+                      int window, int keep_first, cudaStream_t st) {
+    const int groups = (H / G + DM_ROWS - 1) / DM_ROWS;
+    const size_t smem = (size_t)(DM_ROWS * (D + 8) + 2 * MK * (D + 8) + 2 * MK * (DV + 8)) * sizeof(bf16);
+    auto kern = window_attn_decode_mma_kernel<D, DV>;
+    if (smem > 48 * 1024) NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid(G * groups, B);
+    kern<<<grid, DM_THREADS, smem, st>>>((const bf16*)q, (const bf16*)ck, (const bf16*)cv, ka, va, (bf16*)out, positions,
+                                         seq_ids, slopes, H, G, scale, window, keep_first, groups);
+    NXD_LAUNCH_CHECK();
+    return 0;
+}
+
 CacheAddr make_addr(long long stride_line, long long stride_head, const int* block_table, int page_size, int table_cols,
                     int row_dim) {
     CacheAddr a;
@@ -642,12 +879,27 @@ NXD_API int nxd_window_attn_decode(int dtype, const void* q, const void* cache_k
                                    long long k_stride_line, long long k_stride_head, long long v_stride_line,
                                    long long v_stride_head, const int* block_table, int page_size, int table_cols,
                                    void* out, const int* positions, const int* seq_ids, const float* slopes, int B, int H,
-                                   int G, int D, int Dv, float scale, int window, int keep_first, void* stream) {
+                                   int G, int D, int Dv, float scale, int window, int keep_first, int impl, void* stream) {
     NXD_REQUIRE(G > 0 && H % G == 0, "window attention: %d query heads over %d key/value heads", H, G);
     NXD_REQUIRE(Dv <= DEC_MV * 32, "window attention: value size %d above %d", Dv, DEC_MV * 32);
     if (B == 0) return 0;
     const CacheAddr ka = make_addr(k_stride_line, k_stride_head, block_table, page_size, table_cols, D);
     const CacheAddr va = make_addr(v_stride_line, v_stride_head, block_table, page_size, table_cols, Dv);
+    if (dtype == 0 && impl != 1 && (k_stride_head % 8) == 0 && (v_stride_head % 8) == 0 && (k_stride_line % 8) == 0 &&
+        (v_stride_line % 8) == 0) {
+#define NXD_WD_CASE(DD, DDV)                                                                                          \
+    if (D == DD && Dv == DDV)                                                                                         \
+        return launch_decode_mma<DD, DDV>(q, cache_k, cache_v, ka, va, out, positions, seq_ids, slopes, B, H, G, scale, \
+                                          window, keep_first, (cudaStream_t)stream)
+        NXD_WD_CASE(32, 32);
+        NXD_WD_CASE(64, 64);
+        NXD_WD_CASE(96, 96);
+        NXD_WD_CASE(128, 128);
+        NXD_WD_CASE(64, 128);
+        NXD_WD_CASE(128, 64);
+#undef NXD_WD_CASE
+    }
+    NXD_REQUIRE(impl != 2, "window attention decode: no tensor-core kernel for bf16=%d D=%d Dv=%d", dtype == 0, D, Dv);
     if (dtype == 0)
         return launch_decode<bf16>(q, cache_k, cache_v, ka, va, out, positions, seq_ids, slopes, B, H, G, D, Dv, scale,
                                    window, keep_first, (cudaStream_t)stream);

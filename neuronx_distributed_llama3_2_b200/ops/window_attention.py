@@ -177,7 +177,8 @@ def window_attention_prefill(q: torch.Tensor, cache_k: torch.Tensor, cache_v: to
 def window_attention_decode(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor, positions: torch.Tensor,
                             scale: float, window: Optional[int] = None, keep_first: int = 0,
                             slopes: Optional[torch.Tensor] = None, seq_ids: Optional[torch.Tensor] = None,
-                            block_table: Optional[torch.Tensor] = None, page_size: int = 0) -> torch.Tensor:
+                            block_table: Optional[torch.Tensor] = None, page_size: int = 0,
+                            impl: str = "auto") -> torch.Tensor:
     """One new token per row: ``q [B, H, D]`` at ``positions[b]`` -> ``[B, H, Dv]``; only the kept first rows and the
     window's rows of the cache line are read."""
     B, H, D = q.shape
@@ -192,7 +193,8 @@ def window_attention_decode(q: torch.Tensor, cache_k: torch.Tensor, cache_v: tor
         rc = L.nxd_window_attn_decode(_c.c_int(_code(q.dtype)), _lib.ptr(q), _lib.ptr(cache_k), _lib.ptr(cache_v), *cargs,
                                       _lib.ptr(out), _lib.ptr(pos), _lib.ptr(sid), _lib.ptr(slopes), _c.c_int(B),
                                       _c.c_int(H), _c.c_int(G), _c.c_int(D), _c.c_int(Dv), _c.c_float(scale), _c.c_int(w),
-                                      _c.c_int(keep_first), _lib.stream_ptr())
+                                      _c.c_int(keep_first), _c.c_int({"auto": 0, "generic": 1, "mma": 2}[impl]),
+                                      _lib.stream_ptr())
         _lib.check(rc, "nxd_window_attn_decode", L)
         return out
     out = torch.empty(B, H, Dv, dtype=q.dtype, device=q.device)

@@ -188,7 +188,7 @@ def test_tensor_core_prefill_kernel(D, Dv, H, G, size, keep, paged):
     """The bf16 tensor-core prefill against the oracle: unequal rows with padding, a portion that starts inside the
     sequence, tiles that are skipped, keys planted at the edges."""
     dev, dt, scale, S, ps = "cuda", torch.bfloat16, 0.17, 320, 16
-    lens, starts = [300, 77, 1], [0, 150, 0]
+    lens, starts = [300, 227, 1], [0, 150, 0]
     T = max(n - s for n, s in zip(lens, starts))
     w = size if size is not None else 10 ** 6
     torch.manual_seed(D + Dv)
@@ -226,6 +226,18 @@ def test_tensor_core_prefill_kernel(D, Dv, H, G, size, keep, paged):
         close(out[b, :n], ref, dt, scale=25.0)
         close(gen[b, :n], ref, dt, scale=25.0)
         assert float(out[b, n:].float().abs().sum()) == 0.0
+    # one new token per row over the same cache: the tensor-core decode kernel and the generic one
+    for back in (0, 1, 2, 3):
+        pos = [max(n - 1 - back, 0) for n in lens]
+        qd = torch.stack([seqs[b][0][pos[b]] for b in range(3)]).to(dev)
+        dargs = (qd, ck.to(dev), cv.to(dev), torch.tensor(pos, device=dev), scale, size, keep, wa.distance_slopes(H, device=dev))
+        dkw = dict(seq_ids=torch.tensor(lines, device=dev), **kw)
+        dm = wa.window_attention_decode(*dargs, impl="mma", **dkw)
+        dg = wa.window_attention_decode(*dargs, impl="generic", **dkw)
+        for b, (qq, kk, vv) in enumerate(seqs):
+            ref = O.attention_vectorised(qq.to(F64), kk.to(F64), vv.to(F64), H, G, scale, size, keep)[pos[b]]
+            close(dm[b], ref, dt, scale=25.0)
+            close(dg[b], ref, dt, scale=25.0)
 
 
 @case
@@ -313,7 +325,7 @@ def test_prefill_matches_oracle_and_token_by_token_decoding(dev, dt, cfg):
 @pytest.mark.parametrize("portion", [2, 5, 16])
 def test_portions_of_a_prompt(dev, dt, portion):
     cfg = config()
-    toks = tokens_of(cfg, 41, 2)
+    toks = tokens_of(cfg, 41, 6)
     model, sd = build(cfg, dev, dt)
     ref = O.forward(cfg, sd, toks)
     steps, places = [], []

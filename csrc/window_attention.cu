@@ -213,12 +213,12 @@ window_attn_prefill_kernel(const T* __restrict__ q, const T* __restrict__ cache_
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// Tensor-core prefill for bf16 with compile-time head sizes (multiples of 16): 128 queries of one head per CTA (16 per
+// Tensor-core prefill for bf16 with compile-time head sizes (multiples of 16): 64 queries of one head per CTA (16 per
 // warp, mma.sync m16n8k16), key / value tiles of 64 cache rows double-buffered with cp.async, rows padded by 16 bytes
 // in shared memory (ldmatrix without bank conflicts for any D that is a multiple of 16), scores, bias, mask and the
 // online softmax in fp32 registers, P handed to the PV product as A fragments without leaving registers.  The key
 // tiles visited are the ones that hold kept first tokens plus the ones the window of some query of the tile reaches.
-constexpr int MQ = 128, MK = 64, M_THREADS = 256;
+constexpr int MQ = 64, MK = 64, M_THREADS = 128;
 
 template <int D, int DV>
 __global__ void __launch_bounds__(M_THREADS)

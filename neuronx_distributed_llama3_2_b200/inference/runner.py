@@ -342,3 +342,13 @@ class DbrxRunner(InferenceRunner):
 
         kw.setdefault("model_cls", DbrxInferenceModel)
         super().__init__(*a, **kw)
+
+
+class GekazenRunner(InferenceRunner):
+    """Runner of the Gekazen family (``models/gekazen.py``): same buckets, graphs and generate loop."""
+
+    def __init__(self, *a, **kw):
+        from .model import GekazenInferenceModel
+
+        kw.setdefault("model_cls", GekazenInferenceModel)
+        super().__init__(*a, **kw)

@@ -6,3 +6,4 @@ from .mixtral import (MixtralConfig, MixtralForCausalLM, convert_mixtral_hf_stat
 from .gpt_neox import GPTNeoXConfig, GPTNeoXForCausalLM, codegen25_7b, gpt_neox_20b, tiny_gpt_neox  # noqa: F401
 from .bert import BertConfig, BertForPreTraining, bert_large, convert_bert_hf_state_dict, tiny_bert  # noqa: F401
 from .dbrx import DbrxConfig, DbrxForCausalLM, convert_dbrx_hf_state_dict, dbrx_instruct, tiny_dbrx  # noqa: F401
+from .gekazen import GekazenConfig, GekazenForCausalLM, convert_gekazen_state_dict, tiny_gekazen  # noqa: F401

@@ -46,6 +46,9 @@ class SparseMoE(torch.nn.Module):
             self.shared_gate = LinearRouter(hidden_size, 1, dtype=torch.float32, device=dev)
 
     def _use_sorted(self, n_tokens: int) -> bool:
+        # the sorted path reads the per-expert counts on the host: not while a CUDA graph is being captured
+        if torch.cuda.is_available() and torch.cuda.is_current_stream_capturing():
+            return False
         return n_tokens * self.top_k / max(self.num_experts, 1) >= SORTED_PATH_MIN_PAIRS_PER_EXPERT
 
     def forward(self, h: torch.Tensor, path: Optional[str] = None) -> torch.Tensor:

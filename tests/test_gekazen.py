@@ -426,6 +426,35 @@ def test_greedy_generation_through_generate_and_the_continuous_batcher(dev, dt):
         assert res[rid][0] == w[0]
 
 
+@case
+def test_runner_buckets_match_oracle_greedy(dev, dt):
+    """``InferenceRunner`` with the family's model class: prompts padded to a bucket, batch padded to the compiled batch
+    (CUDA graphs on the GPU), greedy continuation equal to the oracle's."""
+    from neuronx_distributed_llama3_2_b200.inference import GekazenRunner
+
+    cfg = config()
+    sd = O.random_weights(cfg, seed=12)
+    gc = GekazenConfig.from_dict(cfg, torch_dtype=dt)
+    ic = InferenceConfig(batch_size=3, max_context_length=32, seq_len=64, buckets=[16, 32], max_new_tokens=5,
+                         use_cuda_graphs=dev == "cuda")
+    runner = GekazenRunner(gc, ic, checkpoint_loader=lambda: convert_gekazen_state_dict(sd, gc), device=torch.device(dev))
+    runner.trace()
+    prompts = [tokens_of(cfg, n, 40 + n) for n in (11, 5)]
+    ids = torch.zeros(2, 11, dtype=torch.long)
+    mask = torch.zeros(2, 11, dtype=torch.long)
+    for b, p in enumerate(prompts):
+        ids[b, :len(p)], mask[b, :len(p)] = torch.tensor(p), 1
+    out = runner.generate(ids.to(dev), mask.to(dev), max_new_tokens=5)
+    runner.close()
+    for b, p in enumerate(prompts):
+        seq = list(p)
+        for _ in range(5):
+            seq.append(int(O.forward(cfg, sd, seq)[-1].argmax()))
+        got = out[b, len(p):len(p) + 5].tolist()
+        assert got[0] == seq[len(p)]
+        assert got == seq[len(p):] or dt != torch.float32, (got, seq[len(p):])
+
+
 def test_registry_and_command_line_replay(tmp_path):
     """``bin/trace_run`` on a model directory: family chosen from config.json, steps on stdin, logits in files."""
     from safetensors.torch import save_file

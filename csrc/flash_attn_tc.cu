@@ -39,6 +39,9 @@ struct TcParams {
     int pos_q[3], pos_k[3], pos_v[3], pos_o[3];  // coordinate slot (1..3) of (row, head, batch) in each tensor map
     float scale_log2;
     DropParams drop;
+    // WIN instantiation only: sliding window with kept first keys and a linear distance bias (causal)
+    int window, keep_first;      // window <= 0: no window
+    const float* slopes;         // [Hq] or NULL; the bias is -slope * (query position - key position)
 };
 
 template <int D>
@@ -55,7 +58,11 @@ struct TcSmem {
     static constexpr int kTmemCols = 256;   // O (D) + S (64) + bf16 P as the tensor-memory A operand of P V (32)
 };
 
-template <int D, bool CAUSAL, bool DROP>
+// WIN: the key tiles a CTA visits are the ones that hold kept first keys followed by the ones its queries' windows reach
+// (`tile(j)` maps the j-th visited tile to its index; every role derives it from the same two numbers), the masked path
+// also hides keys below the window that are not kept, and scores get the scale and the distance bias before the running
+// max (which is then kept in log2 units).  The barrier protocol and the MMA issue are the same for both instantiations.
+template <int D, bool CAUSAL, bool DROP, bool WIN = false>
 __global__ void __launch_bounds__(kThreadsTc, 2)
 fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
@@ -86,6 +93,13 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const int offset = p.Sk - p.Sq;
     int n_tiles = (p.Sk + kBN - 1) / kBN;
     if (CAUSAL) n_tiles = min(n_tiles, max((m0 + kBM + offset + kBN - 1) / kBN, 0));
+    int n_sink = 0, t_win = 0;
+    if (WIN && p.window > 0) {
+        t_win = min(max(0, m0 + offset - p.window + 1) / kBN, n_tiles);
+        n_sink = min((p.keep_first + kBN - 1) / kBN, t_win);
+        n_tiles = n_tiles - t_win + n_sink;
+    }
+    auto tile = [&](int j) { return WIN ? (j < n_sink ? j : t_win + (j - n_sink)) : j; };
 
     if (warp == 0 && lane == 0) {
         ptx::prefetch_tensormap(&tmap_q);
@@ -138,10 +152,10 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 }
                 ++it;
             };
-            load(&tmap_k, p.pos_k, 0);
+            load(&tmap_k, p.pos_k, tile(0) * kBN);
             for (int j = 0; j < n_tiles; ++j) {
-                if (j + 1 < n_tiles) load(&tmap_k, p.pos_k, (j + 1) * kBN);
-                load(&tmap_v, p.pos_v, j * kBN);
+                if (j + 1 < n_tiles) load(&tmap_k, p.pos_k, tile(j + 1) * kBN);
+                load(&tmap_v, p.pos_v, tile(j) * kBN);
             }
         }
     } else if (warp == 1) {
@@ -197,6 +211,8 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         // Running max in RAW score units (the scale is positive, so max commutes with it); the exponent argument is one
         // FFMA per element: s * scale_log2 - m * scale_log2.
         float m_run = -INFINITY, l_run = 0.f;
+        const float sc = WIN ? 1.f : p.scale_log2;                   // WIN: scores are converted to log2 units up front
+        const float slope2 = (WIN && p.slopes != nullptr) ? p.slopes[hq] * 1.4426950408889634f : 0.f;
         // one tile of the online softmax; MASK is instantiated only for tiles on the causal diagonal / past Sk
         auto tile_softmax = [&](auto mask_tag, int j) {
             constexpr bool MASK = decltype(mask_tag)::value;
@@ -206,14 +222,24 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             ptx::tmem_ld_wait();
             ptx::tcgen05_fence_before();
             ptx::mbar_arrive(s_empty);
-            const int n0 = j * kBN;
+            const int n0 = tile(j) * kBN;
+            if (WIN) {
+                // log2 units: s * scale - slope * (query position - key position)
+                const float base = -slope2 * (float)(grow + offset - n0);
+#pragma unroll
+                for (int c = 0; c < kBN; ++c)
+                    sr[c] = __float_as_uint(fmaf(__uint_as_float(sr[c]), p.scale_log2, fmaf(slope2, (float)c, base)));
+            }
             if (MASK) {
                 // columns c >= first_bad are masked: beyond the causal diagonal of this row, or beyond the sequence end
                 int first_bad = p.Sk - n0;
                 if (CAUSAL) first_bad = min(first_bad, grow + offset + 1 - n0);
+                // WIN: columns below the window that are not kept first keys are masked as well
+                const int first_good = (WIN && p.window > 0) ? grow + offset - p.window + 1 - n0 : 0;
+                const int kept = WIN ? p.keep_first - n0 : 0;
 #pragma unroll
                 for (int c = 0; c < kBN; ++c)
-                    if (c >= first_bad) sr[c] = 0xff800000u;   // -inf
+                    if (c >= first_bad || (WIN && c < first_good && c >= kept)) sr[c] = 0xff800000u;   // -inf
             }
             float mx0 = __uint_as_float(sr[0]), mx1 = __uint_as_float(sr[1]), mx2 = __uint_as_float(sr[2]),
                   mx3 = __uint_as_float(sr[3]);
@@ -228,21 +254,21 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             // lazy rescale: keep the stale max unless it moved by more than 2^8 (in scaled log2 units)
             float alpha = 1.f;
             bool rescale = false;
-            if ((mx - m_run) * p.scale_log2 > kRescaleThreshold || m_run == -INFINITY) {
+            if ((mx - m_run) * sc > kRescaleThreshold || m_run == -INFINITY) {
                 const float m_new = fmaxf(m_run, mx);
                 if (m_new != -INFINITY) {
-                    alpha = ex2_approx((m_run - m_new) * p.scale_log2);   // 0 when m_run was -inf
+                    alpha = ex2_approx((m_run - m_new) * sc);   // 0 when m_run was -inf
                     rescale = (j > 0) && (m_run != -INFINITY);
                     m_run = m_new;
                 }
             }
-            const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run * p.scale_log2;
+            const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run * sc;
             float rs0 = 0.f, rs1 = 0.f;
             uint32_t pk[kBN / 2];
 #pragma unroll
             for (int c = 0; c < kBN; c += 2) {
-                const float p0 = ex2_approx(fmaf(__uint_as_float(sr[c]), p.scale_log2, neg_m));
-                const float p1 = ex2_approx(fmaf(__uint_as_float(sr[c + 1]), p.scale_log2, neg_m));
+                const float p0 = ex2_approx(fmaf(__uint_as_float(sr[c]), sc, neg_m));
+                const float p1 = ex2_approx(fmaf(__uint_as_float(sr[c + 1]), sc, neg_m));
                 rs0 += p0;
                 rs1 += p1;
                 if (DROP) {   // the row sum (softmax denominator) is taken before dropout, the PV operand after it
@@ -283,9 +309,12 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         for (int j = 0; j < n_tiles; ++j) {
             ptx::mbar_wait(s_full, (uint32_t)j & 1u);
             ptx::tcgen05_fence_after();
-            const int n0 = j * kBN;
-            // warp-uniform: the tile crosses the sequence end, or the causal diagonal of one of this warp's 32 rows
-            const bool need_mask = (n0 + kBN > p.Sk) || (CAUSAL && (n0 + kBN - 1 > m0 + q * 32 + offset));
+            const int n0 = tile(j) * kBN;
+            // warp-uniform: the tile crosses the sequence end, or the causal diagonal of one of this warp's 32 rows,
+            // or (WIN) the lower edge of the window of one of them while not all of it is kept
+            const bool need_mask = (n0 + kBN > p.Sk) || (CAUSAL && (n0 + kBN - 1 > m0 + q * 32 + offset)) ||
+                                   (WIN && p.window > 0 && m0 + q * 32 + 31 + offset - p.window + 1 > n0 &&
+                                    n0 + kBN > p.keep_first);
             if (need_mask) tile_softmax(std::true_type{}, j);
             else tile_softmax(std::false_type{}, j);
         }
@@ -296,7 +325,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
         if (p.lse && grow < p.Sq)
-            p.lse[((long long)b * p.Hq + hq) * p.Sq + grow] = l_run > 0.f ? m_run * p.scale_log2 + log2f(l_run) : INFINITY;
+            p.lse[((long long)b * p.Hq + hq) * p.Sq + grow] = l_run > 0.f ? m_run * sc + log2f(l_run) : INFINITY;
         // every MMA that read Q has completed: reuse the Q tile as staging (warp q owns rows [32q, 32q+32) of
         // each 64-column group: 32 rows x 128 bytes = one TMA store box)
 #pragma unroll 1
@@ -362,6 +391,19 @@ int launch_fwd_tc(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMa
                 : launch_fwd_tc_one<D, false, false>(tq, tk, tv, to, p, st);
 }
 
+template <int D>
+int launch_fwd_tc_win(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to,
+                      const TcParams& p, cudaStream_t st) {
+    using L = TcSmem<D>;
+    dim3 grid(p.Hq, p.B, (p.Sq + kBM - 1) / kBM);
+    static cudaError_t once = cudaFuncSetAttribute(fa_fwd_tc_kernel<D, true, false, true>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes);
+    NXD_CHECK_CUDA(once);
+    fa_fwd_tc_kernel<D, true, false, true><<<grid, kThreadsTc, L::kBytes, st>>>(tq, tk, tv, to, p);
+    NXD_LAUNCH_CHECK();
+    return 0;
+}
+
 }  // namespace
 
 // Same arguments as nxd_flash_attn_fwd.  Extra requirement: 16-byte aligned base pointers.
@@ -406,4 +448,35 @@ NXD_API int nxd_flash_attn_fwd_tc_dropout(const void* q, const void* k, const vo
                                           float scale, int causal, float dropout_p, unsigned long long seed,
                                           void* stream) {
     return fwd_tc_impl(q, k, v, o, lse, strides, B, Hq, Hkv, Sq, Sk, D, scale, causal, dropout_p, seed, stream);
+}
+
+// Causal attention with a sliding window (window <= 0: none), `keep_first` first keys that stay visible, and a linear
+// distance bias -slopes[h] * (i - j) (slopes NULL: none); tensors and strides as nxd_flash_attn_fwd_tc, no lse output.
+NXD_API int nxd_flash_attn_fwd_tc_window(const void* q, const void* k, const void* v, void* o, const long long* strides,
+                                         int B, int Hq, int Hkv, int Sq, int Sk, int D, float scale, int window,
+                                         int keep_first, const float* slopes, void* stream) {
+    NXD_REQUIRE(D == 64 || D == 128, "flash_attn_tc_window: head dim %d not supported (64 or 128)", D);
+    NXD_REQUIRE(B > 0 && Hq > 0 && Hkv > 0 && Sq > 0 && Sk >= Sq && Hq % Hkv == 0, "flash_attn_tc_window: bad problem");
+    for (int i = 0; i < 12; ++i)
+        NXD_REQUIRE(strides[i] % 8 == 0, "flash_attn_tc_window: stride %d (=%lld) must be a multiple of 8 elements", i,
+                    strides[i]);
+    NXD_REQUIRE((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o) & 15) == 0,
+                "flash_attn_tc_window: tensors must be 16-byte aligned");
+    TcParams p{};
+    p.lse = nullptr;
+    p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Sq = Sq; p.Sk = Sk;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.drop.threshold = 0u;
+    p.drop.inv_keep = 1.f;
+    p.window = window;
+    p.keep_first = keep_first > 0 ? keep_first : 0;
+    p.slopes = slopes;
+    CUtensorMap tq, tk, tv, to;
+    int rc;
+    if ((rc = make_tmap_bhsd(&tq, q, D, Sq, Hq, B, strides[2], strides[1], strides[0], kBM, p.pos_q))) return rc;
+    if ((rc = make_tmap_bhsd(&tk, k, D, Sk, Hkv, B, strides[5], strides[4], strides[3], kBN, p.pos_k))) return rc;
+    if ((rc = make_tmap_bhsd(&tv, v, D, Sk, Hkv, B, strides[8], strides[7], strides[6], kBN, p.pos_v))) return rc;
+    if ((rc = make_tmap_bhsd(&to, o, D, Sq, Hq, B, strides[11], strides[10], strides[9], 32, p.pos_o))) return rc;
+    return D == 64 ? launch_fwd_tc_win<64>(tq, tk, tv, to, p, (cudaStream_t)stream)
+                   : launch_fwd_tc_win<128>(tq, tk, tv, to, p, (cudaStream_t)stream);
 }

@@ -44,7 +44,7 @@ __global__ void qk_norm_cache_write_kernel(const T* __restrict__ qkv, long long 
                                            T* __restrict__ cache_k, T* __restrict__ cache_v, CacheAddr ka, CacheAddr va,
                                            const int* __restrict__ q_start, const int* __restrict__ n_new,
                                            const int* __restrict__ seq_ids, long long units, int Tn, int H, int G, int D,
-                                           int Dv, int has_kv, int normalize, float eps, int max_pos) {
+                                           int Dv, int has_kv, int normalize, float eps, int max_pos, int writeback) {
     const int lane = threadIdx.x & 31;
     const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (unit >= units) return;
@@ -84,7 +84,14 @@ __global__ void qk_norm_cache_write_kernel(const T* __restrict__ qkv, long long 
         ss = warp_sum(ss);
         r = 1.f / sqrtf(ss / (float)dim + eps);
     }
-    for (int i = lane; i < dim; i += 32) stf(dst + i, ldf(src + i) * r);
+    // writeback: the normalised keys also replace the raw ones in the projection buffer, so that a kernel that reads
+    // q / k / v as strided views of that buffer (prefill from position 0) sees what the cache holds
+    T* back = (writeback && hd >= H && hd < H + G) ? const_cast<T*>(src) : nullptr;
+    for (int i = lane; i < dim; i += 32) {
+        const float v = ldf(src + i) * r;
+        stf(dst + i, v);
+        if (back != nullptr) stf(back + i, v);
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -817,7 +824,8 @@ NXD_API int nxd_qk_norm_cache_write(int dtype, const void* qkv, long long ld, vo
                                     long long k_stride_line, long long k_stride_head, long long v_stride_line,
                                     long long v_stride_head, const int* block_table, int page_size, int table_cols,
                                     const int* q_start, const int* n_new, const int* seq_ids, int B, int Tn, int H, int G,
-                                    int D, int Dv, int has_kv, int normalize, float eps, int max_pos, void* stream) {
+                                    int D, int Dv, int has_kv, int normalize, float eps, int max_pos, int writeback,
+                                    void* stream) {
     const long long units = (long long)B * Tn * (H + (has_kv ? 2 * G : 0));
     if (units == 0) return 0;
     const CacheAddr ka = make_addr(k_stride_line, k_stride_head, block_table, page_size, table_cols, D);
@@ -827,11 +835,11 @@ NXD_API int nxd_qk_norm_cache_write(int dtype, const void* qkv, long long ld, vo
     if (dtype == 0)
         qk_norm_cache_write_kernel<bf16><<<blocks, wpb * 32, 0, (cudaStream_t)stream>>>(
             (const bf16*)qkv, ld, (bf16*)q_out, (bf16*)cache_k, (bf16*)cache_v, ka, va, q_start, n_new, seq_ids, units, Tn,
-            H, G, D, Dv, has_kv, normalize, eps, max_pos);
+            H, G, D, Dv, has_kv, normalize, eps, max_pos, writeback);
     else
         qk_norm_cache_write_kernel<float><<<blocks, wpb * 32, 0, (cudaStream_t)stream>>>(
             (const float*)qkv, ld, (float*)q_out, (float*)cache_k, (float*)cache_v, ka, va, q_start, n_new, seq_ids, units,
-            Tn, H, G, D, Dv, has_kv, normalize, eps, max_pos);
+            Tn, H, G, D, Dv, has_kv, normalize, eps, max_pos, writeback);
     NXD_LAUNCH_CHECK();
     return 0;
 }

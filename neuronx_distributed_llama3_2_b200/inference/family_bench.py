@@ -162,6 +162,12 @@ def kernel_cases(s: dict, steps: int, warmup: int, dev) -> List[dict]:
     row("window_attn_prefill_mma (plain causal, bias)", "prefill attention", ms, flops=4.0 * D * pairs_causal * H * B)
     qh = q.permute(0, 2, 1, 3)
     kh, vh = ck[:B, :, :T], cv[:B, :, :T]
+    ms = timer(lambda: wa.window_attention_tc(qh, kh, vh, D ** -0.5, win, keep, slopes), steps, warmup)
+    row("windowed flash attention (tcgen05; window, kept tokens, bias)", "prefill attention", ms,
+        flops=4.0 * D * pairs_win * H * B)
+    ms = timer(lambda: wa.window_attention_tc(qh, kh, vh, D ** -0.5, None, 0, slopes), steps, warmup)
+    row("windowed flash attention (tcgen05; plain causal, bias)", "prefill attention", ms,
+        flops=4.0 * D * pairs_causal * H * B)
     ms = timer(lambda: attn_ops.flash_attn_func(qh, kh, vh, causal=True), steps, warmup)
     row("flash attention forward (tcgen05, plain causal)", "prefill attention", ms, flops=4.0 * D * pairs_causal * H * B)
     # decode attention: bytes of the cache rows that have to be read

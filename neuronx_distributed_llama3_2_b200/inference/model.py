@@ -291,13 +291,16 @@ class KVCacheInferenceMixin:
     def forward_infer(self, input_ids: torch.Tensor, position_ids: torch.Tensor, seq_ids: Optional[torch.Tensor] = None,
                       last_token_index: Optional[torch.Tensor] = None, return_logits: bool = False,
                       uniform: Optional[torch.Tensor] = None, return_hidden: bool = False,
-                      logit_index: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, sample: bool = True):
+                      logit_index: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, sample: bool = True,
+                      past_context: bool = False):
         """``input_ids [B, T]``; ``position_ids [B, T]`` absolute positions; ``seq_ids [B]`` cache lines (default
         ``arange(B)``); ``last_token_index [B]`` index (within T) of the last real prompt token (context encoding with
         right padding).  Returns sampled tokens ``[B]`` (and the ``[B, V]`` logits with ``return_logits``).
         ``logit_index = (rows, cols)``: logits are computed at those ``N`` (row, token) places instead of the last
         token of every row (scoring a prompt, replaying a trace) -> ``[N, V]``; ``sample=False`` skips the sampler and
-        returns ``None`` for the tokens."""
+        returns ``None`` for the tokens.  ``past_context``: a multi-token step whose rows continue sequences that
+        already have tokens in the cache (``position_ids`` do not start at 0); only families whose prefill reads the
+        cache accept it."""
         assert self.kv_cache is not None, "call init_kv_cache() first"
         B, T = input_ids.shape
         prefill = T > 1
@@ -305,6 +308,10 @@ class KVCacheInferenceMixin:
         # replayed with the same static tensor objects but new contents, so the conversion has to be part of every
         # forward (and of every capture)
         self._decode_i32_memo = None
+        if past_context and T > 1 and not getattr(self, "supports_prefill_at_offset", False):
+            raise ValueError("this model family cannot continue a prompt in portions")
+        self._step_past_context = bool(past_context)
+        self._step_kv = {}
         # how many of the T rows are real tokens (right padding), for layers that must not write padding into the cache
         self._step_new_tokens = ((last_token_index + 1).to(torch.int32) if (prefill and last_token_index is not None)
                                  else None)
@@ -492,6 +499,7 @@ class GekazenInferenceModel(KVCacheInferenceMixin, GekazenForCausalLM):
     """
 
     supports_prefill_at_offset = True
+    TC_PREFILL_MIN_TOKENS = 128          # shorter steps stay on the cache-reading kernels
 
     def __init__(self, config: GekazenConfig, inference_config: Optional[InferenceConfig] = None, device=None):
         GekazenForCausalLM.__init__(self, config, device=device)
@@ -535,9 +543,24 @@ class GekazenInferenceModel(KVCacheInferenceMixin, GekazenForCausalLM):
         paged = dict(block_table=kc.block_table, page_size=kc.page_size) if kc.paged else {}
         q_start = positions[:, 0]
         n_new = self._step_new_tokens if prefill else None
-        q = wa_ops.qk_norm_cache_write(attn.qkv_proj(h), ck if owns else None, cv if owns else None, q_start, m.heads,
-                                       m.kv_heads, m.dim, m.vdim, cfg.rms_norm_eps, n_new=n_new, seq_ids=seq_ids, **paged)
-        if T == 1:
+        qkv = attn.qkv_proj(h)
+        # prompts that start at position 0 on the tcgen05 kernel: q / k / v are read as views of the projection output
+        # (the normalised keys are written back into it), nothing is read from the cache
+        src = m.kv_from if m.kv_from is not None else i
+        tc = (T >= self.TC_PREFILL_MIN_TOKENS and not self._step_past_context
+              and wa_ops.tc_prefill_applies(qkv, m.dim, m.vdim, qkv.shape[-1]) and (owns or src in self._step_kv))
+        q = wa_ops.qk_norm_cache_write(qkv, ck if owns else None, cv if owns else None, q_start, m.heads,
+                                       m.kv_heads, m.dim, m.vdim, cfg.rms_norm_eps, n_new=n_new, seq_ids=seq_ids,
+                                       writeback=tc and owns, **paged)
+        if tc and owns:
+            hd = m.heads * m.dim
+            self._step_kv[i] = (qkv[..., hd: hd + m.kv_heads * m.dim].reshape(B, T, m.kv_heads, m.dim).permute(0, 2, 1, 3),
+                                qkv[..., hd + m.kv_heads * m.dim:].reshape(B, T, m.kv_heads, m.vdim).permute(0, 2, 1, 3))
+        if tc:
+            kv, vv = self._step_kv[src]
+            o = wa_ops.window_attention_tc(q.permute(0, 2, 1, 3), kv, vv, m.scale, m.window, m.keep_first, attn.slopes)
+            o = o.permute(0, 2, 1, 3)
+        elif T == 1:
             o = wa_ops.window_attention_decode(q[:, 0], ck, cv, q_start, m.scale, m.window, m.keep_first, attn.slopes,
                                                seq_ids=seq_ids, **paged)
         else:

@@ -76,7 +76,8 @@ class TraceReplayer:
             last = torch.tensor(counts, dtype=torch.long) - 1
             _, logits = self.model.forward_infer(
                 ids.to(dev), pos.to(dev), seq_ids=lines.to(dev), last_token_index=last.to(dev), return_logits=True,
-                logit_index=(torch.tensor(rows, device=dev), torch.tensor(cols, device=dev)), sample=False)
+                logit_index=(torch.tensor(rows, device=dev), torch.tensor(cols, device=dev)), sample=False,
+                past_context=T > 1 and any(s != 0 for s in starts))
             for b, e in enumerate(entries):
                 self.length[e["id"]] = starts[b] + counts[b]
             if any(e["want"] for e in entries):

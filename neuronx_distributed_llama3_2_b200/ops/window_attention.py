@@ -62,15 +62,17 @@ def qk_norm_cache_write(qkv: torch.Tensor, cache_k: Optional[torch.Tensor], cach
                         q_start: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int, eps: float,
                         n_new: Optional[torch.Tensor] = None, seq_ids: Optional[torch.Tensor] = None,
                         normalize: bool = True, block_table: Optional[torch.Tensor] = None,
-                        page_size: int = 0) -> torch.Tensor:
+                        page_size: int = 0, writeback: bool = False) -> torch.Tensor:
     """``qkv [B, T, heads*dim (+ kv_heads*dim + kv_heads*vdim)]`` -> ``q [B, T, heads, dim]``; with a cache given the
     key and value heads of the real rows (``t < n_new[b]``) are written at position ``q_start[b] + t`` of cache line
     ``seq_ids[b]``.  ``normalize``: queries and keys are divided by their root mean square over ``dim`` (fp32, ``eps``
-    inside the root) before they are written."""
+    inside the root) before they are written.  ``writeback``: the normalised keys of the real rows also replace the
+    raw ones inside ``qkv`` (for a kernel that reads q / k / v as strided views of the projection output)."""
     B, T, n_out = qkv.shape
     has_kv = cache_k is not None
     assert n_out == heads * dim + (kv_heads * (dim + vdim) if has_kv else 0), (n_out, heads, kv_heads, dim, vdim)
     if _use_kernel(qkv):
+        assert qkv.is_contiguous() or not writeback
         qkv = qkv if qkv.is_contiguous() else qkv.contiguous()
         q = torch.empty(B, T, heads, dim, dtype=qkv.dtype, device=qkv.device)
         qs, nn_, sid = _i32(q_start), _i32(n_new), _i32(seq_ids)
@@ -83,7 +85,7 @@ def qk_norm_cache_write(qkv: torch.Tensor, cache_k: Optional[torch.Tensor], cach
                                        _lib.ptr(ck), _lib.ptr(cv), *cargs, _lib.ptr(qs), _lib.ptr(nn_), _lib.ptr(sid),
                                        _c.c_int(B), _c.c_int(T), _c.c_int(heads), _c.c_int(kv_heads), _c.c_int(dim),
                                        _c.c_int(vdim), _c.c_int(int(has_kv)), _c.c_int(int(normalize)), _c.c_float(eps),
-                                       _c.c_int(max_pos), _lib.stream_ptr())
+                                       _c.c_int(max_pos), _c.c_int(int(writeback and has_kv)), _lib.stream_ptr())
         _lib.check(rc, "nxd_qk_norm_cache_write", L)
         return q
 
@@ -101,6 +103,8 @@ def qk_norm_cache_write(qkv: torch.Tensor, cache_k: Optional[torch.Tensor], cach
             n = T if n_new is None else int(n_new[b])
             line = b if seq_ids is None else int(seq_ids[b])
             p0 = int(q_start[b])
+            if writeback:
+                qkv[b, :n, heads * dim: (heads + kv_heads) * dim] = k[b, :n].reshape(n, kv_heads * dim)
             for t in range(n):
                 pos = p0 + t
                 if block_table is not None:
@@ -206,3 +210,33 @@ def window_attention_decode(q: torch.Tensor, cache_k: torch.Tensor, cache_v: tor
         out[b] = window_attention_ref(q[b:b + 1], kk, vv, torch.tensor([p], device=q.device), scale, w, keep_first,
                                       slopes)[0].to(q.dtype)
     return out
+
+
+def tc_prefill_applies(q: torch.Tensor, dim: int, vdim: int, n_out: int) -> bool:
+    """The tcgen05 windowed prefill kernel serves bf16 on the GPU, equal key and value size of 64 or 128, and projection
+    rows whose pitch keeps every head 16-byte aligned."""
+    from . import backend
+
+    return (q.is_cuda and q.dtype == torch.bfloat16 and dim == vdim and dim in (64, 128) and n_out % 8 == 0
+            and backend.attn_backend() == "nxd" and _lib.available())
+
+
+def window_attention_tc(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, window: Optional[int] = None,
+                        keep_first: int = 0, slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Prefill from position 0 on the tcgen05 flash-attention kernel (``csrc/flash_attn_tc.cu``, windowed
+    instantiation): ``q [B, H, T, D]``, ``k / v [B, G, T, D]`` as (strided) views with unit stride on ``D`` ->
+    ``[B, H, T, D]`` stored as ``[B, T, H, D]``.  All rows are taken as ``T`` tokens long (right padding only ever
+    sits behind the real tokens of a causal row)."""
+    from .flash_attn import _fix, _strides
+
+    q, k, v = _fix(q), _fix(k), _fix(v)
+    B, H, T, D = q.shape
+    G = k.shape[1]
+    o = torch.empty(B, T, H, D, dtype=q.dtype, device=q.device).permute(0, 2, 1, 3)
+    L = _lib.lib()
+    rc = L.nxd_flash_attn_fwd_tc_window(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _strides(q, k, v, o),
+                                        _c.c_int(B), _c.c_int(H), _c.c_int(G), _c.c_int(T), _c.c_int(T), _c.c_int(D),
+                                        _c.c_float(scale), _c.c_int(int(window) if window else 0), _c.c_int(keep_first),
+                                        _lib.ptr(slopes), _lib.stream_ptr())
+    _lib.check(rc, "nxd_flash_attn_fwd_tc_window")
+    return o

@@ -240,6 +240,53 @@ def test_tensor_core_prefill_kernel(D, Dv, H, G, size, keep, paged):
             close(dg[b], ref, dt, scale=25.0)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("D,H,G,size,keep,T", [(64, 4, 2, 100, 5, 300), (128, 2, 2, None, 0, 200), (64, 2, 1, 130, 70, 513),
+                                               (128, 4, 1, 1, 1, 129), (64, 4, 4, 64, 64, 260), (128, 2, 1, 200, 3, 700)])
+def test_tcgen05_windowed_prefill(D, H, G, size, keep, T):
+    """The windowed instantiation of the tcgen05 flash-attention kernel (tile schedule, window mask, distance bias) on
+    strided views of one projection buffer, against the oracle; keys planted at the window's and the kept tokens' edges."""
+    dev, dt, scale = "cuda", torch.bfloat16, 0.21
+    w = size if size is not None else 10 ** 6
+    outs = []
+    for qi in (T - 1, T - 70, 140):
+        qi = max(min(qi, T - 1), 8)
+        plant = [(qi, max(qi - w + 1, 0)), (qi - 1, max(qi - 1 - w, 0)), (qi - 2, max(keep - 1, 0)), (qi - 3, min(keep, qi - 3))]
+        q, k, v = [t.to(dt) for t in _planted(T, H, G, D, D, plant)]
+        buf = torch.cat([q.reshape(T, H * D), k.reshape(T, G * D), v.reshape(T, G * D)], dim=1).unsqueeze(0).to(dev)
+        qv = buf[..., :H * D].reshape(1, T, H, D).permute(0, 2, 1, 3)
+        kv = buf[..., H * D:(H + G) * D].reshape(1, T, G, D).permute(0, 2, 1, 3)
+        vv = buf[..., (H + G) * D:].reshape(1, T, G, D).permute(0, 2, 1, 3)
+        out = wa.window_attention_tc(qv, kv, vv, scale, size, keep, wa.distance_slopes(H, device=dev))
+        ref = O.attention_vectorised(q.to(F64), k.to(F64), v.to(F64), H, G, scale, size, keep)
+        close(out[0].permute(1, 0, 2), ref, dt, scale=25.0)
+        outs.append(out)
+
+
+@pytest.mark.gpu
+def test_model_prefill_on_the_tcgen05_path_matches_oracle():
+    """Head size 64 and prompts of 128+ tokens take the tcgen05 prefill (views of the projection output, normalised
+    keys written back, a layer that reuses another layer's keys and values); decoding continues from the cache."""
+    dt, dev = torch.bfloat16, "cuda"
+    cfg = config(layers=[
+        {"type": "attention", "mixer": mixer(heads=4, kv_heads=2, dim=64, vdim=64, mask={"size": 40, "keep_first": 3}), "mlp": mlp()},
+        {"type": "attention", "mixer": mixer(heads=4, kv_heads=2, dim=64, vdim=64, kv_from=0, mask={"size": 90, "keep_first": 0}),
+         "mlp": None},
+        {"type": "attention", "mixer": mixer(heads=2, kv_heads=1, dim=64, vdim=64, mask=None), "mlp": mlp(shared=None)},
+    ], width=64)
+    model, sd = build(cfg, dev, dt, lines=3, seq_len=256)
+    toks = {k: tokens_of(cfg, n, 50 + n) for k, n in (("a", 200), ("b", 150))}
+    ref = {k: O.forward(cfg, sd, v) for k, v in toks.items()}
+    steps = [([{"id": "a", "tokens": toks["a"][:190], "want": [0, 39, 40, 41, 100, 189]},
+               {"id": "b", "tokens": toks["b"][:131], "want": [2, 3, 4, 130]}], [])]
+    for s in range(10):
+        steps.append(([{"id": "a", "tokens": [toks["a"][190 + s]], "want": [0]},
+                       {"id": "b", "tokens": [toks["b"][131 + s]], "want": [0]}], []))
+    got = replay(model, steps)
+    check_rows(got["a"], ref["a"], [0, 39, 40, 41, 100, 189] + list(range(190, 200)), dt)
+    check_rows(got["b"], ref["b"], [2, 3, 4, 130] + list(range(131, 141)), dt)
+
+
 @case
 def test_window_attention_paged_cache_and_padding(dev, dt):
     torch.manual_seed(3)

@@ -183,7 +183,8 @@ def test_window_attention_prefill_and_decode_edges(dev, dt, size, keep):
 @pytest.mark.gpu
 @pytest.mark.parametrize("D,Dv,H,G,size,keep,paged", [(32, 32, 4, 2, 12, 3, False), (64, 64, 4, 4, 100, 5, True),
                                                        (96, 96, 2, 1, 70, 0, False), (128, 128, 2, 2, None, 0, True),
-                                                       (64, 128, 2, 1, 130, 70, False), (128, 64, 4, 2, 1, 1, False)])
+                                                       (64, 128, 2, 1, 130, 70, False), (128, 64, 4, 2, 1, 1, False),
+                                                       (32, 32, 40, 2, 50, 2, False)])
 def test_tensor_core_prefill_kernel(D, Dv, H, G, size, keep, paged):
     """The bf16 tensor-core prefill against the oracle: unequal rows with padding, a portion that starts inside the
     sequence, tiles that are skipped, keys planted at the edges."""
@@ -530,3 +531,31 @@ def test_registry_and_command_line_replay(tmp_path):
     a = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").reshape(2, cfg["vocab"]))
     b = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4").reshape(1, cfg["vocab"]))
     check_rows([a[0], a[1], b[0]], ref, [0, 14, 16], torch.float32)
+
+
+def test_replayer_and_registry_serve_the_llama_family_too(tmp_path):
+    """The registry picks the Llama model for an HF-style config.json, and the trace replayer drives it through the same
+    step function: a request inside an unequal batch equals the request alone, decoding continues from the cache,
+    and portions of a prompt are refused by a family whose prefill does not read the cache."""
+    from neuronx_distributed_llama3_2_b200.inference.registry import families, load_model
+
+    assert {"llama", "gekazen"} <= set(families())
+    (tmp_path / "config.json").write_text(json.dumps({
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama", "vocab_size": 128, "hidden_size": 64,
+        "intermediate_size": 128, "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2,
+        "head_dim": 16, "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "rope_scaling": None,
+        "max_position_embeddings": 256, "tie_word_embeddings": True}))
+    ic = InferenceConfig(batch_size=4, max_batch_size=4, max_context_length=64, seq_len=64, is_continuous_batching=True,
+                         use_cuda_graphs=False)
+    torch.manual_seed(0)
+    model = load_model(str(tmp_path), dtype=torch.float32, inference_config=ic, device=torch.device("cpu"),
+                       load_weights=False)
+    toks = tokens_of({"vocab": 128}, 20, 1)
+    rp = TraceReplayer(model)
+    a = rp.step([{"id": "x", "tokens": toks[:12], "want": [0, 11]}, {"id": "y", "tokens": toks[:5], "want": [4]}], [])
+    b = rp.step([{"id": "x", "tokens": toks[12:13], "want": [0]}, {"id": "y", "tokens": toks[5:6], "want": [0]}], ["y", "x"])
+    c = rp.step([{"id": "z", "tokens": toks[:13], "want": [0, 11, 12]}], [])
+    assert float((a[0] - c[0]).abs().max()) < 1e-5 and float((a[1] - c[1]).abs().max()) < 1e-5
+    assert float((b[0] - c[2]).abs().max()) < 1e-4
+    with pytest.raises(ValueError):
+        rp.step([{"id": "z", "tokens": toks[13:16], "want": [0]}], [])

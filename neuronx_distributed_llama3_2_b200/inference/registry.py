@@ -24,6 +24,7 @@ class ModelFamily:
     make_config: Callable[[Dict[str, Any], torch.dtype], Any]
     model_cls: Callable[[], type]                                   # lazy: importing a family costs nothing until used
     convert_state_dict: Callable[[Dict[str, torch.Tensor], Any], Dict[str, torch.Tensor]]
+    kernel_group: Optional[str] = None        # ``ops._lib.GROUPS`` entry that holds every kernel the family's serving needs
 
 
 _FAMILIES: List[ModelFamily] = []
@@ -88,7 +89,8 @@ def _gekazen_cls():
 
 
 register_family(ModelFamily("llama", lambda c: _arch(c).startswith("llama"), _llama_config, _llama_cls, _llama_convert))
-register_family(ModelFamily("gekazen", lambda c: _arch(c) == "gekazen", _gekazen_config, _gekazen_cls, _gekazen_convert))
+register_family(ModelFamily("gekazen", lambda c: _arch(c) == "gekazen", _gekazen_config, _gekazen_cls, _gekazen_convert,
+                            kernel_group="window_moe_serving"))
 
 
 def read_config(model_dir: str) -> Dict[str, Any]:
@@ -103,6 +105,10 @@ def load_model(model_dir: str, dtype: torch.dtype = torch.bfloat16, inference_co
 
     raw = read_config(model_dir)
     fam = resolve(raw)
+    if fam.kernel_group is not None:
+        from ..ops import _lib
+
+        _lib.prefer_group(fam.kernel_group)     # a fresh checkout then compiles this family's kernels only
     cfg = fam.make_config(raw, dtype)
     device = device or (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available()
                         else torch.device("cpu"))

@@ -44,10 +44,39 @@ NVCC_FLAGS = [
 GROUPS = {
     "window_moe": ["window_attention.cu", "post_norm.cu", "moe_sparse.cu", "runtime.cu"],
 }
+# everything a bf16 serving step of the window / sparse-MoE families touches: their own kernels, the GEMM kernels behind
+# the linear layers, and the tcgen05 flash attention that the windowed prefill is an instantiation of
+GROUPS["window_moe_serving"] = GROUPS["window_moe"] + [
+    "gemm_tcgen05.cu", "gemm_smallm.cu", "fused_gemm_ar.cu", "tma_host.cu", "flash_attn_tc.cu", "attn_tc_host.cu"]
 
 _lib: Optional[ctypes.CDLL] = None
 _group_libs = {}
+_preferred_group: Optional[str] = None
 _lock = threading.Lock()
+
+
+def prefer_group(group: Optional[str]) -> None:
+    """A program that serves one family only (a command-line tool) names the kernel group it needs: while the full
+    library is not built, every ``lib()`` call is answered from that group's library, so a fresh checkout compiles
+    that group and nothing else.  An entry point that the group does not hold falls through to the full library."""
+    global _preferred_group
+    assert group is None or group in GROUPS, group
+    _preferred_group = group
+
+
+class _GroupLibrary:
+    """A group's library that hands every entry point it does not have to the full library (built on that first miss)."""
+
+    def __init__(self, handle: ctypes.CDLL):
+        self._handle = handle
+
+    def __getattr__(self, name):
+        try:
+            fn = getattr(self._handle, name)
+        except AttributeError:
+            fn = getattr(_full_lib(), name)
+        setattr(self, name, fn)
+        return fn
 launch_count = 0  # number of our kernels' entry points invoked (bench "gpu_launches")
 
 
@@ -129,17 +158,30 @@ def build(force: bool = False, verbose: bool = False, group: Optional[str] = Non
 def lib(group: Optional[str] = None) -> ctypes.CDLL:
     """The kernel library.  ``group``: a library that holds at least that kernel group -- the full one when it is
     loaded or built and current, else the group's own small library (built on first use)."""
-    global _lib
     if _lib is not None:
         return _lib
+    group = _preferred_group or group
     if group is not None and "NXD_B200_LIB" not in os.environ and _stale():
         with _lock:
             handle = _group_libs.get(group)
             if handle is None:
-                handle = ctypes.CDLL(build(group=group))
-                handle.nxd_last_error.restype = ctypes.c_char_p
-                _group_libs[group] = handle
-        return handle
+                try:
+                    cdll = ctypes.CDLL(build(group=group))
+                    cdll.nxd_last_error.restype = ctypes.c_char_p
+                    handle = _GroupLibrary(cdll)
+                except OSError:          # a source of the group needs a symbol from outside it: use the full library
+                    handle = None
+                if handle is not None:
+                    _group_libs[group] = handle
+        if handle is not None:
+            return handle
+    return _full_lib()
+
+
+def _full_lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
     with _lock:
         if _lib is None:
             if not os.path.exists(LIB_PATH):
@@ -171,7 +213,7 @@ def available(group: Optional[str] = None) -> bool:
 def kernel_launches() -> int:
     """Kernel launches made by the library in this process so far (counted at every ``<<<>>>`` in csrc/)."""
     total = 0
-    for handle in ([_lib] if _lib is not None else []) + list(_group_libs.values()) or [lib()]:
+    for handle in ([_lib] if _lib is not None else []) + [g._handle for g in _group_libs.values()] or [lib()]:
         fn = handle.nxd_kernel_launches
         fn.restype = ctypes.c_ulonglong
         total += int(fn())

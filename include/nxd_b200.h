@@ -280,6 +280,48 @@ int nxd_decode_qkv_rope_cache(const void* x, long long ldx, const void* norm_w, 
 int nxd_decode_gate_up_swiglu(const void* x, long long ldx, const void* norm_w, float eps, const void* w, long long ldw,
                               void* out, long long ldo, int B, int K, int I, void* stream);
 
+/* ---- windowed attention over the KV cache, post-norm residual, sparse MoE (no counterpart in the reference) -----------
+ * dtype arguments: 0 = bf16, 1 = fp32.  Cache: contiguous [lines, G, S, D] (block_table NULL) or paged
+ * [pages, G, page_size, D] with block_table [lines, table_cols]; strides in elements.
+ * visible(i, j) = j <= i and (window <= 0 or i - j < window or j < keep_first);
+ * score(i, j) = scale * <q_i, k_j> - slopes[h] * (i - j)  (slopes NULL: no bias). */
+int nxd_qk_norm_cache_write(int dtype, const void* qkv, long long ld, void* q_out, void* cache_k, void* cache_v,
+                            long long k_stride_line, long long k_stride_head, long long v_stride_line,
+                            long long v_stride_head, const int* block_table, int page_size, int table_cols,
+                            const int* q_start, const int* n_new, const int* seq_ids, int B, int Tn, int H, int G, int D,
+                            int Dv, int has_kv, int normalize, float eps, int max_pos, int writeback, void* stream);
+/* impl: 0 = choose, 1 = generic kernel, 2 = mma.sync kernel (error when it does not apply) */
+int nxd_window_attn_prefill(int dtype, const void* q, const void* cache_k, const void* cache_v, long long k_stride_line,
+                            long long k_stride_head, long long v_stride_line, long long v_stride_head,
+                            const int* block_table, int page_size, int table_cols, void* out, const int* q_start,
+                            const int* n_new, const int* seq_ids, const float* slopes, int B, int Tn, int H, int G, int D,
+                            int Dv, float scale, int window, int keep_first, int impl, void* stream);
+int nxd_window_attn_decode(int dtype, const void* q, const void* cache_k, const void* cache_v, long long k_stride_line,
+                           long long k_stride_head, long long v_stride_line, long long v_stride_head,
+                           const int* block_table, int page_size, int table_cols, void* out, const int* positions,
+                           const int* seq_ids, const float* slopes, int B, int H, int G, int D, int Dv, float scale,
+                           int window, int keep_first, int impl, void* stream);
+/* tcgen05 flash attention with window / kept first keys / distance bias; tensors and strides as nxd_flash_attn_fwd_tc */
+int nxd_flash_attn_fwd_tc_window(const void* q, const void* k, const void* v, void* o, const long long* strides, int B,
+                                 int Hq, int Hkv, int Sq, int Sk, int D, float scale, int window, int keep_first,
+                                 const float* slopes, void* stream);
+/* n = y / sqrt(mean(y^2) + eps) * (offset + w);  x (fp32, may be NULL) += n in place;  h (may be NULL) = cast(x or n) */
+int nxd_post_norm_residual(int y_dtype, int w_dtype, int h_dtype, const void* y, const void* w, float* x, void* h,
+                           long long rows, int W, float eps, float offset, void* stream);
+/* router: s = softmax(wr h); the `top` largest (s + corr) are chosen, weight = s * out_scale; sgate = sigmoid(<wsg, h>) */
+int nxd_moe_router(int dtype, const void* h, const float* wr, const float* corr, const float* wsg, int* idx, float* wts,
+                   float* sgate, long long N, int W, int R, int top, float out_scale, void* stream);
+/* expert weights [E, in, out]; an index outside [0, E) is an identity expert */
+int nxd_moe_gate_up_act(int dtype, const void* h, const void* wgu, const int* idx, void* act, long long P,
+                        int pairs_per_token, int W, int F, int E, float limit, float alpha, void* stream);
+int nxd_moe_down_combine(int dtype, const void* act, const void* wd, const int* idx, const float* wts, const void* h,
+                         const void* act_s, const void* wds, const float* sgate, float* y, long long N, int top, int W,
+                         int F, int Fs, int E, void* stream);
+int nxd_clamped_glu(int dtype, const void* gate_up, void* out, long long M, int F, float limit, float alpha, void* stream);
+int nxd_moe_gather_combine(int dtype, const void* ys, const int* slot, const int* idx, const float* wts, const void* h,
+                           const void* shared_out, const float* sgate, float* y, long long N, int top, int W, int E,
+                           void* stream);
+
 #ifdef __cplusplus
 }
 #endif

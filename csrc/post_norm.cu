@@ -74,6 +74,70 @@ int launch(const void* y, const void* w, float* x, void* h, long long rows, int 
     return 0;
 }
 
+
+// Pre- and post-norm of one sublayer boundary in a single pass over an fp32 residual stream:
+//
+//   (y given)       x <- x + norm(y) * w_post                  (norm on the sublayer's output, x in place)
+//   (w_next given)  h  = cast(norm(x) * w_next)                (the next sublayer's input)
+//
+// norm(v) = (v - mean(v)) / sqrt(var(v) + eps) with center != 0 (layer norm, weight only), v / sqrt(mean(v^2) + eps)
+// otherwise.  One CTA per row; the row sits in shared memory, mean and variance are two separate fp32 reductions.
+template <typename TY, typename TH>
+__global__ void __launch_bounds__(PN_THREADS)
+norm_chain_kernel(const TY* __restrict__ y, const float* __restrict__ w_post, float* __restrict__ x,
+                  const float* __restrict__ w_next, TH* __restrict__ h, int W, float eps, int center) {
+    extern __shared__ float rowbuf[];
+    __shared__ float red[32];
+    const long long row = blockIdx.x;
+    float* xr = x + row * W;
+    if (y != nullptr) {
+        const TY* yr = y + row * W;
+        float s = 0.f;
+        for (int c = threadIdx.x; c < W; c += PN_THREADS) {
+            const float v = ldf(yr + c);
+            rowbuf[c] = v;
+            s += v;
+        }
+        const float mean = center ? block_sum(s, red) / (float)W : 0.f;
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < W; c += PN_THREADS) {
+            const float d = rowbuf[c] - mean;
+            ss += d * d;
+        }
+        const float r = 1.f / sqrtf(block_sum(ss, red) / (float)W + eps);
+        for (int c = threadIdx.x; c < W; c += PN_THREADS) {
+            const float v = xr[c] + (rowbuf[c] - mean) * r * w_post[c];
+            xr[c] = v;
+            rowbuf[c] = v;
+        }
+    } else {
+        for (int c = threadIdx.x; c < W; c += PN_THREADS) rowbuf[c] = xr[c];
+    }
+    if (w_next == nullptr || h == nullptr) return;
+    float s = 0.f;
+    for (int c = threadIdx.x; c < W; c += PN_THREADS) s += rowbuf[c];
+    const float mean = center ? block_sum(s, red) / (float)W : 0.f;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < W; c += PN_THREADS) {
+        const float d = rowbuf[c] - mean;
+        ss += d * d;
+    }
+    const float r = 1.f / sqrtf(block_sum(ss, red) / (float)W + eps);
+    TH* hr = h + row * W;
+    for (int c = threadIdx.x; c < W; c += PN_THREADS) stf(hr + c, (rowbuf[c] - mean) * r * w_next[c]);
+}
+
+template <typename TY, typename TH>
+int launch_chain(const void* y, const float* w_post, float* x, const float* w_next, void* h, long long rows, int W,
+                 float eps, int center, cudaStream_t st) {
+    const size_t smem = (size_t)W * sizeof(float);
+    auto kern = norm_chain_kernel<TY, TH>;
+    if (smem > 48 * 1024) NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<(unsigned)rows, PN_THREADS, smem, st>>>((const TY*)y, w_post, x, w_next, (TH*)h, W, eps, center);
+    NXD_LAUNCH_CHECK();
+    return 0;
+}
+
 }  // namespace
 
 // y [rows, W] (y_dtype), w [W] (w_dtype), x [rows, W] fp32 or NULL, h [rows, W] (h_dtype) or NULL; dtypes: 0 bf16,
@@ -93,5 +157,21 @@ NXD_API int nxd_post_norm_residual(int y_dtype, int w_dtype, int h_dtype, const 
         case 5: return launch<float, bf16, float>(y, w, x, h, rows, W, eps, offset, st);
         case 6: return launch<float, float, bf16>(y, w, x, h, rows, W, eps, offset, st);
         default: return launch<float, float, float>(y, w, x, h, rows, W, eps, offset, st);
+    }
+}
+
+// x [rows, W] fp32 stream (updated in place when y is given); y [rows, W] (y_dtype) or NULL; w_post, w_next [W] fp32 (or
+// NULL); h [rows, W] (h_dtype) or NULL.  center: 1 = layer norm (mean removed), 0 = RMS norm.
+NXD_API int nxd_norm_chain(int y_dtype, int h_dtype, const void* y, const float* w_post, float* x, const float* w_next,
+                           void* h, long long rows, int W, float eps, int center, void* stream) {
+    if (rows == 0) return 0;
+    NXD_REQUIRE(rows < (1ll << 31), "norm chain: %lld rows", rows);
+    NXD_REQUIRE((size_t)W * sizeof(float) <= 200 * 1024, "norm chain: width %d", W);
+    cudaStream_t st = (cudaStream_t)stream;
+    switch ((y_dtype << 1) | h_dtype) {
+        case 0: return launch_chain<bf16, bf16>(y, w_post, x, w_next, h, rows, W, eps, center, st);
+        case 1: return launch_chain<bf16, float>(y, w_post, x, w_next, h, rows, W, eps, center, st);
+        case 2: return launch_chain<float, bf16>(y, w_post, x, w_next, h, rows, W, eps, center, st);
+        default: return launch_chain<float, float>(y, w_post, x, w_next, h, rows, W, eps, center, st);
     }
 }

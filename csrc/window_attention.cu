@@ -2,7 +2,12 @@
 // per-head query/key size D and value size Dv that need not be equal or a power of two; bf16 or fp32 activations.
 //
 //   visible(i, j) = j <= i and (window <= 0 or i - j < window or j < keep_first)
+//                   and (chunk <= 0 or floor(i / chunk) == floor(j / chunk))
 //   score(i, j)   = scale * <q_i, k_j> - slope_h * (i - j)            (slopes == NULL: no bias)
+//   softmax denominator = sum over visible j of exp(score) (+ exp(sink_h) with sinks != NULL: a learned per-head
+//                   logit attached to no position that only takes probability mass)
+// Chunk boundaries sit at absolute multiples of the chunk size.  The value rows may be a column range of the key rows (one
+// cache tensor, value row pitch = key row pitch): the latent cache of a compressed key/value projection.
 //
 // Kernels:
 //   window_attn_prefill_mma  bf16, head sizes from a compiled list: tensor-core prefill (see below); the generic prefill
@@ -44,7 +49,10 @@ __global__ void qk_norm_cache_write_kernel(const T* __restrict__ qkv, long long 
                                            T* __restrict__ cache_k, T* __restrict__ cache_v, CacheAddr ka, CacheAddr va,
                                            const int* __restrict__ q_start, const int* __restrict__ n_new,
                                            const int* __restrict__ seq_ids, long long units, int Tn, int H, int G, int D,
-                                           int Dv, int has_kv, int normalize, float eps, int max_pos, int writeback) {
+                                           int Dv, int has_kv, int normalize, float eps, int max_pos, int writeback,
+                                           const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+                                           const float* __restrict__ rope_cos, const float* __restrict__ rope_sin,
+                                           int rope_dims, int value_from_key) {
     const int lane = threadIdx.x & 31;
     const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (unit >= units) return;
@@ -60,6 +68,9 @@ __global__ void qk_norm_cache_write_kernel(const T* __restrict__ qkv, long long 
     } else if (hd < H + G) {
         src = qkv + n * ld + (long long)H * D + (long long)(hd - H) * D;
         dim = D;
+    } else if (value_from_key) {             // the raw key projections double as values: no value columns in the row
+        src = qkv + n * ld + (long long)H * D + (long long)(hd - H - G) * D;
+        dim = Dv;
     } else {
         src = qkv + n * ld + (long long)(H + G) * D + (long long)(hd - H - G) * Dv;
         dim = Dv;
@@ -87,15 +98,34 @@ __global__ void qk_norm_cache_write_kernel(const T* __restrict__ qkv, long long 
     // writeback: the normalised keys also replace the raw ones in the projection buffer, so that a kernel that reads
     // q / k / v as strided views of that buffer (prefill from position 0) sees what the cache holds
     T* back = (writeback && hd >= H && hd < H + G) ? const_cast<T*>(src) : nullptr;
-    for (int i = lane; i < dim; i += 32) {
-        const float v = ldf(src + i) * r;
+    const float* wgt = hd < H ? q_weight : (hd < H + G ? k_weight : nullptr);
+    const int rot = (hd < H + G && rope_cos != nullptr) ? rope_dims : 0;
+    // rotated part: the pair (2i, 2i + 1) turns by the angle of (position, i); cos / sin come from a table [pos][i]
+    if (rot > 0) {
+        const long long pos = (long long)q_start[b] + t;
+        const float* cs = rope_cos + pos * (rope_dims / 2);
+        const float* sn = rope_sin + pos * (rope_dims / 2);
+        for (int i = lane; i < rot / 2; i += 32) {
+            float u = ldf(src + 2 * i) * r, v = ldf(src + 2 * i + 1) * r;
+            if (wgt != nullptr) {
+                u *= wgt[2 * i];
+                v *= wgt[2 * i + 1];
+            }
+            const float c = cs[i], s = sn[i];
+            stf(dst + 2 * i, u * c - v * s);
+            stf(dst + 2 * i + 1, v * c + u * s);
+        }
+    }
+    for (int i = rot + lane; i < dim; i += 32) {
+        float v = ldf(src + i) * r;
+        if (wgt != nullptr) v *= wgt[i];
         stf(dst + i, v);
         if (back != nullptr) stf(back + i, v);
     }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-constexpr int BQ = 16, BK = 32, PF_THREADS = 128, MAXC = 32;   // MAXC * 8 = largest value size
+constexpr int BQ = 16, BK = 32, PF_THREADS = 128, MAXC = 64;   // MAXC * 8 = largest value size
 
 template <typename T>
 __global__ void __launch_bounds__(PF_THREADS)
@@ -103,7 +133,7 @@ window_attn_prefill_kernel(const T* __restrict__ q, const T* __restrict__ cache_
                            CacheAddr ka, CacheAddr va, T* __restrict__ out, const int* __restrict__ q_start,
                            const int* __restrict__ n_new, const int* __restrict__ seq_ids,
                            const float* __restrict__ slopes, int Tn, int H, int G, int D, int Dv, float scale, int window,
-                           int keep_first) {
+                           int keep_first, int chunk, const float* __restrict__ sinks) {
     extern __shared__ float smem[];
     float* Qs = smem;                       // [BQ][D]
     float* Ks = Qs + BQ * D;                // [BK][D + 1]
@@ -147,6 +177,7 @@ window_attn_prefill_kernel(const T* __restrict__ q, const T* __restrict__ cache_
     for (int kt = 0; kt <= last_tile; ++kt) {
         const int k0 = kt * BK;
         if (window > 0 && k0 >= keep_first && k0 + BK - 1 <= p_lo - window) continue;   // nobody in the tile sees it
+        if (chunk > 0 && k0 + BK - 1 < (p_lo / chunk) * chunk) continue;                 // before every query's chunk
         __syncthreads();                     // previous tile fully consumed (and Qs written, first time round)
         if (tid < BK) {
             const int pos = k0 + tid;
@@ -174,7 +205,8 @@ window_attn_prefill_kernel(const T* __restrict__ q, const T* __restrict__ cache_
             float d = 0.f;
             for (int c = 0; c < D; ++c) d = fmaf(qr[c], kr[c], d);
             const int dist = p_i - j;
-            const bool vis = row_ok && dist >= 0 && (window <= 0 || dist < window || j < keep_first);
+            const bool vis = row_ok && dist >= 0 && (window <= 0 || dist < window || j < keep_first) &&
+                             (chunk <= 0 || p_i / chunk == j / chunk);
             s[m] = vis ? d - slope * (float)dist : -INFINITY;
             tmax = fmaxf(tmax, s[m]);
         }
@@ -207,6 +239,7 @@ window_attn_prefill_kernel(const T* __restrict__ q, const T* __restrict__ cache_
             }
         }
     }
+    if (sinks != nullptr) l_i += expf(sinks[h] - (m_i == -INFINITY ? 0.f : m_i));
     if (q0 + qi < Tn) {
         const float inv = (row_ok && l_i > 0.f) ? 1.f / l_i : 0.f;
 #pragma unroll
@@ -233,7 +266,7 @@ window_attn_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restric
                                const bf16* __restrict__ cache_v, CacheAddr ka, CacheAddr va, bf16* __restrict__ out,
                                const int* __restrict__ q_start, const int* __restrict__ n_new,
                                const int* __restrict__ seq_ids, const float* __restrict__ slopes, int Tn, int H, int G,
-                               float scale, int window, int keep_first) {
+                               float scale, int window, int keep_first, int chunk, const float* __restrict__ sinks) {
     constexpr int LDK = D + 8, LDV = DV + 8, CK = D / 8, CV = DV / 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);       // [MQ][LDK]
@@ -261,8 +294,9 @@ window_attn_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restric
     int t_win = 0, n_sink_tiles = 0;
     if (window > 0) {
         t_win = max(0, p_lo - window + 1) / MK;
-        n_sink_tiles = min((keep_first + MK - 1) / MK, t_win);
     }
+    if (chunk > 0) t_win = max(t_win, ((p_lo / chunk) * chunk) / MK);     // tiles before the first query's chunk
+    if (window > 0) n_sink_tiles = min((keep_first + MK - 1) / MK, t_win);
     const int n_tiles = n_sink_tiles + last_tile - t_win + 1;
 
     const uint32_t qs_addr = (uint32_t)__cvta_generic_to_shared(Qs);
@@ -345,7 +379,8 @@ window_attn_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restric
         // scale, distance bias, mask; row maxima.  A tile that every query of the CTA sees completely needs no mask.
         float mx0 = -INFINITY, mx1 = -INFINITY;
         const bool full = q0 + MQ <= nb && k0 + MK - 1 <= p_lo &&
-                          (window <= 0 || p_hi - k0 < window || k0 + MK <= keep_first);
+                          (window <= 0 || p_hi - k0 < window || k0 + MK <= keep_first) &&
+                          (chunk <= 0 || k0 / chunk == p_hi / chunk);
         if (full) {
             const float jb = (float)(k0 + (lane & 3) * 2);
             const float c0 = sl2 * (jb - (float)pi0), c1 = sl2 * (jb - (float)pi1);     // -slope * (i - j) at column 0
@@ -367,7 +402,9 @@ window_attn_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restric
                     const int j = k0 + i * 8 + (lane & 3) * 2 + (e & 1);
                     const int pi = (e & 2) ? pi1 : pi0;
                     const int dist = pi - j;
-                    const bool vis = ((e & 2) ? ok1 : ok0) && dist >= 0 && (window <= 0 || dist < window || j < keep_first);
+                    const bool vis = ((e & 2) ? ok1 : ok0) && dist >= 0 &&
+                                     (window <= 0 || dist < window || j < keep_first) &&
+                                     (chunk <= 0 || pi / chunk == j / chunk);
                     const float v = vis ? s[i][e] * sc2 - sl2 * (float)dist : -INFINITY;
                     s[i][e] = v;
                     if (e & 2) mx1 = fmaxf(mx1, v); else mx0 = fmaxf(mx0, v);
@@ -421,6 +458,11 @@ window_attn_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restric
     }
     l0 = mma::quad_sum(l0);
     l1 = mma::quad_sum(l1);
+    if (sinks != nullptr) {
+        const float sk = sinks[h] * LOG2E;
+        l0 += exp2f(sk - (m0 == -INFINITY ? 0.f : m0));
+        l1 += exp2f(sk - (m1 == -INFINITY ? 0.f : m1));
+    }
     const float i0 = (ok0 && l0 > 0.f) ? 1.f / l0 : 0.f, i1 = (ok1 && l1 > 0.f) ? 1.f / l1 : 0.f;
     bf16* out0 = out + (((long long)b * Tn + q0 + r_lo) * H + h) * DV + (lane & 3) * 2;
     bf16* out1 = out0 + (long long)8 * H * DV;
@@ -434,26 +476,27 @@ window_attn_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restric
 template <int D, int DV>
 int launch_prefill_mma(const void* q, const void* ck, const void* cv, CacheAddr ka, CacheAddr va, void* out,
                        const int* q_start, const int* n_new, const int* seq_ids, const float* slopes, int B, int Tn, int H,
-                       int G, float scale, int window, int keep_first, cudaStream_t st) {
+                       int G, float scale, int window, int keep_first, int chunk, const float* sinks, cudaStream_t st) {
     const size_t smem = (size_t)(MQ * (D + 8) + 2 * MK * (D + 8) + 2 * MK * (DV + 8)) * sizeof(bf16);
     auto kern = window_attn_prefill_mma_kernel<D, DV>;
     if (smem > 48 * 1024) NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((Tn + MQ - 1) / MQ, H, B);
     kern<<<grid, M_THREADS, smem, st>>>((const bf16*)q, (const bf16*)ck, (const bf16*)cv, ka, va, (bf16*)out, q_start,
-                                        n_new, seq_ids, slopes, Tn, H, G, scale, window, keep_first);
+                                        n_new, seq_ids, slopes, Tn, H, G, scale, window, keep_first, chunk, sinks);
     NXD_LAUNCH_CHECK();
     return 0;
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-constexpr int DEC_WARPS = 8, DEC_R = 8, DEC_MV = 8;   // query heads per CTA, value columns per lane (Dv <= 256)
+constexpr int DEC_WARPS = 8;   // DEC_R query heads per CTA, DEC_MV value columns per lane (Dv <= 32 * DEC_MV)
 
-template <typename T>
+template <typename T, int DEC_R, int DEC_MV>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 window_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ cache_k, const T* __restrict__ cache_v,
                           CacheAddr ka, CacheAddr va, T* __restrict__ out, const int* __restrict__ positions,
                           const int* __restrict__ seq_ids, const float* __restrict__ slopes, int H, int G, int D, int Dv,
-                          float scale, int window, int keep_first, int groups_per_kv) {
+                          float scale, int window, int keep_first, int chunk, const float* __restrict__ sinks,
+                          int groups_per_kv) {
     extern __shared__ float smem[];
     const int R_all = H / G;
     const int g = blockIdx.x / groups_per_kv, sub_group = blockIdx.x % groups_per_kv;
@@ -471,8 +514,9 @@ window_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ cache_k
         Qs[idx] = ldf(q + ((long long)b * H + h0 + r) * D + c) * scale;
     }
     __syncthreads();
-    const int lo = window > 0 ? max(0, p - window + 1) : 0;
-    const int n_sink = min(keep_first, lo);
+    const int c_lo = chunk > 0 ? (p / chunk) * chunk : 0;          // first position of the query's chunk
+    const int lo = max(window > 0 ? max(0, p - window + 1) : 0, c_lo);
+    const int n_sink = max(0, min(keep_first, lo) - c_lo);         // kept first tokens below the window, inside the chunk
     const int nk = n_sink + (p - lo + 1);
     float m_r[DEC_R], l_r[DEC_R], sl[DEC_R];
     float acc[DEC_R][DEC_MV];
@@ -485,7 +529,7 @@ window_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ cache_k
         for (int m = 0; m < DEC_MV; ++m) acc[r][m] = 0.f;
     }
     for (int i = warp; i < nk; i += DEC_WARPS) {
-        const int j = i < n_sink ? i : lo + (i - n_sink);
+        const int j = i < n_sink ? c_lo + i : lo + (i - n_sink);
         const T* kr = cache_k + ka.row(line, g, j);
         const T* vr = cache_v + va.row(line, g, j);
         float d[DEC_R];
@@ -548,6 +592,7 @@ window_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ cache_k
             num = fmaf(f, src[c], num);
             den = fmaf(f, src[Dv + 1], den);
         }
+        if (sinks != nullptr) den += expf(sinks[h0 + r] - (mx == -INFINITY ? 0.f : mx));
         stf(out + ((long long)b * H + h0 + r) * Dv + c, den > 0.f ? num / den : 0.f);
     }
 }
@@ -565,7 +610,7 @@ window_attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict
                               const bf16* __restrict__ cache_v, CacheAddr ka, CacheAddr va, bf16* __restrict__ out,
                               const int* __restrict__ positions, const int* __restrict__ seq_ids,
                               const float* __restrict__ slopes, int H, int G, float scale, int window, int keep_first,
-                              int groups_per_kv) {
+                              int chunk, const float* __restrict__ sinks, int groups_per_kv) {
     constexpr int LDK = D + 8, LDV = DV + 8, CK = D / 8, CV = DV / 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);       // [DM_ROWS][LDK]
@@ -585,8 +630,9 @@ window_attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict
     int t_win = 0, n_sink_tiles = 0;
     if (window > 0) {
         t_win = max(0, p - window + 1) / MK;
-        n_sink_tiles = min((keep_first + MK - 1) / MK, t_win);
     }
+    if (chunk > 0) t_win = max(t_win, ((p / chunk) * chunk) / MK);
+    if (window > 0) n_sink_tiles = min((keep_first + MK - 1) / MK, t_win);
     const int n_tiles = n_sink_tiles + last_tile - t_win + 1;
     const uint32_t qs_addr = (uint32_t)__cvta_generic_to_shared(Qs);
     const uint32_t ks_addr = (uint32_t)__cvta_generic_to_shared(Ks);
@@ -667,7 +713,8 @@ window_attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict
             for (int e = 0; e < 4; ++e) {
                 const int j = k0 + i * 8 + (lane & 3) * 2 + (e & 1);
                 const int dist = p - j;
-                const bool vis = ((e & 2) ? ok1 : ok0) && dist >= 0 && (window <= 0 || dist < window || j < keep_first);
+                const bool vis = ((e & 2) ? ok1 : ok0) && dist >= 0 &&
+                                 (window <= 0 || dist < window || j < keep_first) && (chunk <= 0 || p / chunk == j / chunk);
                 const float v = vis ? s[i][e] * sc2 - ((e & 2) ? sl1 : sl0) * (float)dist : -INFINITY;
                 s[i][e] = v;
                 if (e & 2) mx1 = fmaxf(mx1, v); else mx0 = fmaxf(mx0, v);
@@ -753,6 +800,7 @@ window_attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict
             num = fmaf(f, src[c], num);
             den = fmaf(f, src[DV + 1], den);
         }
+        if (sinks != nullptr) den += exp2f(sinks[h0 + r] * LOG2E - (mx == -INFINITY ? 0.f : mx));
         out[((long long)b * H + h0 + r) * DV + c] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
     }
 }
@@ -760,14 +808,14 @@ window_attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict
 template <int D, int DV>
 int launch_decode_mma(const void* q, const void* ck, const void* cv, CacheAddr ka, CacheAddr va, void* out,
                       const int* positions, const int* seq_ids, const float* slopes, int B, int H, int G, float scale,
-                      int window, int keep_first, cudaStream_t st) {
+                      int window, int keep_first, int chunk, const float* sinks, cudaStream_t st) {
     const int groups = (H / G + DM_ROWS - 1) / DM_ROWS;
     const size_t smem = (size_t)(DM_ROWS * (D + 8) + 2 * MK * (D + 8) + 2 * MK * (DV + 8)) * sizeof(bf16);
     auto kern = window_attn_decode_mma_kernel<D, DV>;
     if (smem > 48 * 1024) NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid(G * groups, B);
     kern<<<grid, DM_THREADS, smem, st>>>((const bf16*)q, (const bf16*)ck, (const bf16*)cv, ka, va, (bf16*)out, positions,
-                                         seq_ids, slopes, H, G, scale, window, keep_first, groups);
+                                         seq_ids, slopes, H, G, scale, window, keep_first, chunk, sinks, groups);
     NXD_LAUNCH_CHECK();
     return 0;
 }
@@ -787,13 +835,30 @@ CacheAddr make_addr(long long stride_line, long long stride_head, const int* blo
 template <typename T>
 int launch_prefill(const void* q, const void* ck, const void* cv, CacheAddr ka, CacheAddr va, void* out,
                    const int* q_start, const int* n_new, const int* seq_ids, const float* slopes, int B, int Tn, int H,
-                   int G, int D, int Dv, float scale, int window, int keep_first, cudaStream_t st) {
+                   int G, int D, int Dv, float scale, int window, int keep_first, int chunk, const float* sinks,
+                   cudaStream_t st) {
     const size_t smem = (size_t)(BQ * D + BK * (D + 1) + BK * Dv + BQ * BK) * sizeof(float);
     auto kern = window_attn_prefill_kernel<T>;
     if (smem > 48 * 1024) NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((Tn + BQ - 1) / BQ, H, B);
     kern<<<grid, PF_THREADS, smem, st>>>((const T*)q, (const T*)ck, (const T*)cv, ka, va, (T*)out, q_start, n_new,
-                                         seq_ids, slopes, Tn, H, G, D, Dv, scale, window, keep_first);
+                                         seq_ids, slopes, Tn, H, G, D, Dv, scale, window, keep_first, chunk, sinks);
+    NXD_LAUNCH_CHECK();
+    return 0;
+}
+
+template <typename T, int DEC_R, int DEC_MV>
+int launch_decode_rm(const void* q, const void* ck, const void* cv, CacheAddr ka, CacheAddr va, void* out,
+                     const int* positions, const int* seq_ids, const float* slopes, int B, int H, int G, int D, int Dv,
+                     float scale, int window, int keep_first, int chunk, const float* sinks, cudaStream_t st) {
+    const int R_all = H / G;
+    const int groups = (R_all + DEC_R - 1) / DEC_R;
+    const size_t smem = (size_t)(DEC_R * D + DEC_WARPS * DEC_R * (Dv + 2)) * sizeof(float);
+    auto kern = window_attn_decode_kernel<T, DEC_R, DEC_MV>;
+    if (smem > 48 * 1024) NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid(G * groups, B);
+    kern<<<grid, DEC_WARPS * 32, smem, st>>>((const T*)q, (const T*)ck, (const T*)cv, ka, va, (T*)out, positions, seq_ids,
+                                             slopes, H, G, D, Dv, scale, window, keep_first, chunk, sinks, groups);
     NXD_LAUNCH_CHECK();
     return 0;
 }
@@ -801,17 +866,12 @@ int launch_prefill(const void* q, const void* ck, const void* cv, CacheAddr ka, 
 template <typename T>
 int launch_decode(const void* q, const void* ck, const void* cv, CacheAddr ka, CacheAddr va, void* out,
                   const int* positions, const int* seq_ids, const float* slopes, int B, int H, int G, int D, int Dv,
-                  float scale, int window, int keep_first, cudaStream_t st) {
-    const int R_all = H / G;
-    const int groups = (R_all + DEC_R - 1) / DEC_R;
-    const size_t smem = (size_t)(DEC_R * D + DEC_WARPS * DEC_R * (Dv + 2)) * sizeof(float);
-    auto kern = window_attn_decode_kernel<T>;
-    if (smem > 48 * 1024) NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    dim3 grid(G * groups, B);
-    kern<<<grid, DEC_WARPS * 32, smem, st>>>((const T*)q, (const T*)ck, (const T*)cv, ka, va, (T*)out, positions, seq_ids,
-                                             slopes, H, G, D, Dv, scale, window, keep_first, groups);
-    NXD_LAUNCH_CHECK();
-    return 0;
+                  float scale, int window, int keep_first, int chunk, const float* sinks, cudaStream_t st) {
+    if (Dv <= 256)
+        return launch_decode_rm<T, 8, 8>(q, ck, cv, ka, va, out, positions, seq_ids, slopes, B, H, G, D, Dv, scale, window,
+                                         keep_first, chunk, sinks, st);
+    return launch_decode_rm<T, 4, 16>(q, ck, cv, ka, va, out, positions, seq_ids, slopes, B, H, G, D, Dv, scale, window,
+                                      keep_first, chunk, sinks, st);      // wide value rows: fewer heads per CTA
 }
 
 }  // namespace
@@ -820,14 +880,21 @@ int launch_decode(const void* q, const void* ck, const void* cv, CacheAddr ka, C
 // out as H query heads of D, then (has_kv) G key heads of D and G value heads of Dv.  q_start [B]: position of the first
 // new token of every row; n_new [B] or NULL: how many of the Tn rows are real (the others are padding and write
 // nothing); seq_ids [B] or NULL: cache line of every row.  max_pos: rows of a cache line.
-NXD_API int nxd_qk_norm_cache_write(int dtype, const void* qkv, long long ld, void* q_out, void* cache_k, void* cache_v,
+// q_weight / k_weight [D] fp32 or NULL: weight of the per-head norm.  rope_cos / rope_sin [positions, rope_dims / 2]
+// fp32 or NULL: queries and keys (after the norm) turn pairwise, (2i, 2i + 1), on their first rope_dims dimensions.
+// value_from_key: the row has no value columns, the cached value is the raw key projection (taken ahead of the norm and the rotation).
+NXD_API int nxd_qk_prep_cache_write(int dtype, const void* qkv, long long ld, void* q_out, void* cache_k, void* cache_v,
                                     long long k_stride_line, long long k_stride_head, long long v_stride_line,
                                     long long v_stride_head, const int* block_table, int page_size, int table_cols,
                                     const int* q_start, const int* n_new, const int* seq_ids, int B, int Tn, int H, int G,
                                     int D, int Dv, int has_kv, int normalize, float eps, int max_pos, int writeback,
-                                    void* stream) {
+                                    const float* q_weight, const float* k_weight, const float* rope_cos,
+                                    const float* rope_sin, int rope_dims, int value_from_key, void* stream) {
     const long long units = (long long)B * Tn * (H + (has_kv ? 2 * G : 0));
     if (units == 0) return 0;
+    NXD_REQUIRE(rope_cos == nullptr || (rope_dims % 2 == 0 && rope_dims <= D), "rotation over %d of %d dimensions", rope_dims, D);
+    NXD_REQUIRE(!value_from_key || Dv == D, "values taken from the keys need equal sizes (%d, %d)", D, Dv);
+    NXD_REQUIRE(!(writeback && rope_cos != nullptr), "write-back of rotated keys is not %s", "supported");
     const CacheAddr ka = make_addr(k_stride_line, k_stride_head, block_table, page_size, table_cols, D);
     const CacheAddr va = make_addr(v_stride_line, v_stride_head, block_table, page_size, table_cols, Dv);
     const int wpb = 8;
@@ -835,82 +902,129 @@ NXD_API int nxd_qk_norm_cache_write(int dtype, const void* qkv, long long ld, vo
     if (dtype == 0)
         qk_norm_cache_write_kernel<bf16><<<blocks, wpb * 32, 0, (cudaStream_t)stream>>>(
             (const bf16*)qkv, ld, (bf16*)q_out, (bf16*)cache_k, (bf16*)cache_v, ka, va, q_start, n_new, seq_ids, units, Tn,
-            H, G, D, Dv, has_kv, normalize, eps, max_pos, writeback);
+            H, G, D, Dv, has_kv, normalize, eps, max_pos, writeback, q_weight, k_weight, rope_cos, rope_sin, rope_dims,
+            value_from_key);
     else
         qk_norm_cache_write_kernel<float><<<blocks, wpb * 32, 0, (cudaStream_t)stream>>>(
             (const float*)qkv, ld, (float*)q_out, (float*)cache_k, (float*)cache_v, ka, va, q_start, n_new, seq_ids, units,
-            Tn, H, G, D, Dv, has_kv, normalize, eps, max_pos, writeback);
+            Tn, H, G, D, Dv, has_kv, normalize, eps, max_pos, writeback, q_weight, k_weight, rope_cos, rope_sin, rope_dims,
+            value_from_key);
     NXD_LAUNCH_CHECK();
     return 0;
 }
 
-// q [B, Tn, H, D] -> out [B, Tn, H, Dv]; the keys and values of positions [0, q_start[b] + n_new[b]) are read from the
-// cache (the new tokens' rows must have been written before).  slopes [H] fp32 or NULL; window <= 0: plain causal.
-// impl: 0 = choose, 1 = the generic kernel, 2 = the tensor-core kernel (an error when it does not apply).
-NXD_API int nxd_window_attn_prefill(int dtype, const void* q, const void* cache_k, const void* cache_v,
+NXD_API int nxd_qk_norm_cache_write(int dtype, const void* qkv, long long ld, void* q_out, void* cache_k, void* cache_v,
                                     long long k_stride_line, long long k_stride_head, long long v_stride_line,
                                     long long v_stride_head, const int* block_table, int page_size, int table_cols,
-                                    void* out, const int* q_start, const int* n_new, const int* seq_ids,
-                                    const float* slopes, int B, int Tn, int H, int G, int D, int Dv, float scale,
-                                    int window, int keep_first, int impl, void* stream) {
-    NXD_REQUIRE(G > 0 && H % G == 0, "window attention: %d query heads over %d key/value heads", H, G);
-    NXD_REQUIRE(Dv <= MAXC * 8, "window attention: value size %d above %d", Dv, MAXC * 8);
+                                    const int* q_start, const int* n_new, const int* seq_ids, int B, int Tn, int H, int G,
+                                    int D, int Dv, int has_kv, int normalize, float eps, int max_pos, int writeback,
+                                    void* stream) {
+    return nxd_qk_prep_cache_write(dtype, qkv, ld, q_out, cache_k, cache_v, k_stride_line, k_stride_head, v_stride_line,
+                                   v_stride_head, block_table, page_size, table_cols, q_start, n_new, seq_ids, B, Tn, H, G,
+                                   D, Dv, has_kv, normalize, eps, max_pos, writeback, nullptr, nullptr, nullptr, nullptr, 0,
+                                   0, stream);
+}
+
+// q [B, Tn, H, D] -> out [B, Tn, H, Dv]; the keys and values of positions [0, q_start[b] + n_new[b]) are read from the
+// cache (the new tokens' rows must have been written before).  slopes [H] fp32 or NULL; window <= 0: no window;
+// chunk <= 0: no chunks; sinks [H] fp32 or NULL.  k_row / v_row: elements between consecutive cache rows (D / Dv for
+// tensors of their own; v_row == k_row when the values are columns of the key rows).
+// impl: 0 = choose, 1 = the generic kernel, 2 = the tensor-core kernel (an error when it does not apply).
+NXD_API int nxd_masked_attn_prefill(int dtype, const void* q, const void* cache_k, const void* cache_v,
+                                    long long k_stride_line, long long k_stride_head, long long k_row,
+                                    long long v_stride_line, long long v_stride_head, long long v_row,
+                                    const int* block_table, int page_size, int table_cols, void* out, const int* q_start,
+                                    const int* n_new, const int* seq_ids, const float* slopes, const float* sinks, int B,
+                                    int Tn, int H, int G, int D, int Dv, float scale, int window, int keep_first, int chunk,
+                                    int impl, void* stream) {
+    NXD_REQUIRE(G > 0 && H % G == 0, "attention: %d query heads over %d key/value heads", H, G);
+    NXD_REQUIRE(Dv <= MAXC * 8, "attention: value size %d above %d", Dv, MAXC * 8);
     if (B * Tn == 0) return 0;
-    const CacheAddr ka = make_addr(k_stride_line, k_stride_head, block_table, page_size, table_cols, D);
-    const CacheAddr va = make_addr(v_stride_line, v_stride_head, block_table, page_size, table_cols, Dv);
-    // bf16 with head sizes the tensor-core kernel is compiled for (cache rows must start on 16-byte boundaries, which a
-    // cache tensor with a row size that is a multiple of 8 guarantees); everything else takes the generic kernel
+    const CacheAddr ka = make_addr(k_stride_line, k_stride_head, block_table, page_size, table_cols, (int)k_row);
+    const CacheAddr va = make_addr(v_stride_line, v_stride_head, block_table, page_size, table_cols, (int)v_row);
+    cudaStream_t st = (cudaStream_t)stream;
+    // bf16 with head sizes the tensor-core kernel is compiled for (cache rows must start on 16-byte boundaries);
+    // everything else takes the generic kernel
     if (dtype == 0 && impl != 1 && Tn >= 16 && (k_stride_head % 8) == 0 && (v_stride_head % 8) == 0 &&
-        (k_stride_line % 8) == 0 && (v_stride_line % 8) == 0) {
+        (k_stride_line % 8) == 0 && (v_stride_line % 8) == 0 && (k_row % 8) == 0 && (v_row % 8) == 0 &&
+        ((uintptr_t)cache_k % 16) == 0 && ((uintptr_t)cache_v % 16) == 0) {
 #define NXD_WA_CASE(DD, DDV)                                                                                          \
     if (D == DD && Dv == DDV)                                                                                         \
         return launch_prefill_mma<DD, DDV>(q, cache_k, cache_v, ka, va, out, q_start, n_new, seq_ids, slopes, B, Tn, H, \
-                                           G, scale, window, keep_first, (cudaStream_t)stream)
+                                           G, scale, window, keep_first, chunk, sinks, st)
         NXD_WA_CASE(32, 32);
         NXD_WA_CASE(64, 64);
         NXD_WA_CASE(96, 96);
         NXD_WA_CASE(128, 128);
         NXD_WA_CASE(64, 128);
         NXD_WA_CASE(128, 64);
+        NXD_WA_CASE(96, 64);      // key size = un-rotated + rotated dimensions of an expanded latent head
+        NXD_WA_CASE(192, 128);
 #undef NXD_WA_CASE
     }
-    NXD_REQUIRE(impl != 2, "window attention: no tensor-core kernel for bf16=%d D=%d Dv=%d", dtype == 0, D, Dv);
+    NXD_REQUIRE(impl != 2, "attention: no tensor-core kernel for bf16=%d D=%d Dv=%d", dtype == 0, D, Dv);
     if (dtype == 0)
         return launch_prefill<bf16>(q, cache_k, cache_v, ka, va, out, q_start, n_new, seq_ids, slopes, B, Tn, H, G, D, Dv,
-                                    scale, window, keep_first, (cudaStream_t)stream);
+                                    scale, window, keep_first, chunk, sinks, st);
     return launch_prefill<float>(q, cache_k, cache_v, ka, va, out, q_start, n_new, seq_ids, slopes, B, Tn, H, G, D, Dv,
-                                 scale, window, keep_first, (cudaStream_t)stream);
+                                 scale, window, keep_first, chunk, sinks, st);
+}
+
+NXD_API int nxd_window_attn_prefill(int dtype, const void* q, const void* cache_k, const void* cache_v,
+                                    long long k_stride_line, long long k_stride_head, long long v_stride_line,
+                                    long long v_stride_head, const int* block_table, int page_size, int table_cols,
+                                    void* out, const int* q_start, const int* n_new, const int* seq_ids,
+                                    const float* slopes, int B, int Tn, int H, int G, int D, int Dv, float scale,
+                                    int window, int keep_first, int impl, void* stream) {
+    return nxd_masked_attn_prefill(dtype, q, cache_k, cache_v, k_stride_line, k_stride_head, D, v_stride_line,
+                                   v_stride_head, Dv, block_table, page_size, table_cols, out, q_start, n_new, seq_ids,
+                                   slopes, nullptr, B, Tn, H, G, D, Dv, scale, window, keep_first, 0, impl, stream);
 }
 
 // q [B, H, D] of one new token per row at positions[b] (its key and value already in the cache) -> out [B, H, Dv].
-NXD_API int nxd_window_attn_decode(int dtype, const void* q, const void* cache_k, const void* cache_v,
-                                   long long k_stride_line, long long k_stride_head, long long v_stride_line,
-                                   long long v_stride_head, const int* block_table, int page_size, int table_cols,
-                                   void* out, const int* positions, const int* seq_ids, const float* slopes, int B, int H,
-                                   int G, int D, int Dv, float scale, int window, int keep_first, int impl, void* stream) {
-    NXD_REQUIRE(G > 0 && H % G == 0, "window attention: %d query heads over %d key/value heads", H, G);
-    NXD_REQUIRE(Dv <= DEC_MV * 32, "window attention: value size %d above %d", Dv, DEC_MV * 32);
+NXD_API int nxd_masked_attn_decode(int dtype, const void* q, const void* cache_k, const void* cache_v,
+                                   long long k_stride_line, long long k_stride_head, long long k_row,
+                                   long long v_stride_line, long long v_stride_head, long long v_row,
+                                   const int* block_table, int page_size, int table_cols, void* out, const int* positions,
+                                   const int* seq_ids, const float* slopes, const float* sinks, int B, int H, int G, int D,
+                                   int Dv, float scale, int window, int keep_first, int chunk, int impl, void* stream) {
+    NXD_REQUIRE(G > 0 && H % G == 0, "attention: %d query heads over %d key/value heads", H, G);
+    NXD_REQUIRE(Dv <= 512, "attention: value size %d above %d", Dv, 512);
     if (B == 0) return 0;
-    const CacheAddr ka = make_addr(k_stride_line, k_stride_head, block_table, page_size, table_cols, D);
-    const CacheAddr va = make_addr(v_stride_line, v_stride_head, block_table, page_size, table_cols, Dv);
+    const CacheAddr ka = make_addr(k_stride_line, k_stride_head, block_table, page_size, table_cols, (int)k_row);
+    const CacheAddr va = make_addr(v_stride_line, v_stride_head, block_table, page_size, table_cols, (int)v_row);
+    cudaStream_t st = (cudaStream_t)stream;
     if (dtype == 0 && impl != 1 && (k_stride_head % 8) == 0 && (v_stride_head % 8) == 0 && (k_stride_line % 8) == 0 &&
-        (v_stride_line % 8) == 0) {
+        (v_stride_line % 8) == 0 && (k_row % 8) == 0 && (v_row % 8) == 0 && ((uintptr_t)cache_k % 16) == 0 &&
+        ((uintptr_t)cache_v % 16) == 0) {
 #define NXD_WD_CASE(DD, DDV)                                                                                          \
     if (D == DD && Dv == DDV)                                                                                         \
         return launch_decode_mma<DD, DDV>(q, cache_k, cache_v, ka, va, out, positions, seq_ids, slopes, B, H, G, scale, \
-                                          window, keep_first, (cudaStream_t)stream)
+                                          window, keep_first, chunk, sinks, st)
         NXD_WD_CASE(32, 32);
         NXD_WD_CASE(64, 64);
         NXD_WD_CASE(96, 96);
         NXD_WD_CASE(128, 128);
         NXD_WD_CASE(64, 128);
         NXD_WD_CASE(128, 64);
+        NXD_WD_CASE(160, 128);    // latent rows: compressed key/value + shared rotated key part; value = the compressed part
+        NXD_WD_CASE(288, 256);
 #undef NXD_WD_CASE
     }
-    NXD_REQUIRE(impl != 2, "window attention decode: no tensor-core kernel for bf16=%d D=%d Dv=%d", dtype == 0, D, Dv);
+    NXD_REQUIRE(impl != 2, "attention decode: no tensor-core kernel for bf16=%d D=%d Dv=%d", dtype == 0, D, Dv);
     if (dtype == 0)
         return launch_decode<bf16>(q, cache_k, cache_v, ka, va, out, positions, seq_ids, slopes, B, H, G, D, Dv, scale,
-                                   window, keep_first, (cudaStream_t)stream);
+                                   window, keep_first, chunk, sinks, st);
     return launch_decode<float>(q, cache_k, cache_v, ka, va, out, positions, seq_ids, slopes, B, H, G, D, Dv, scale,
-                                window, keep_first, (cudaStream_t)stream);
+                                window, keep_first, chunk, sinks, st);
+}
+
+NXD_API int nxd_window_attn_decode(int dtype, const void* q, const void* cache_k, const void* cache_v,
+                                   long long k_stride_line, long long k_stride_head, long long v_stride_line,
+                                   long long v_stride_head, const int* block_table, int page_size, int table_cols,
+                                   void* out, const int* positions, const int* seq_ids, const float* slopes, int B, int H,
+                                   int G, int D, int Dv, float scale, int window, int keep_first, int impl, void* stream) {
+    return nxd_masked_attn_decode(dtype, q, cache_k, cache_v, k_stride_line, k_stride_head, D, v_stride_line,
+                                  v_stride_head, Dv, block_table, page_size, table_cols, out, positions, seq_ids, slopes,
+                                  nullptr, B, H, G, D, Dv, scale, window, keep_first, 0, impl, stream);
 }

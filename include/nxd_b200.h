@@ -301,6 +301,50 @@ int nxd_window_attn_decode(int dtype, const void* q, const void* cache_k, const 
                            const int* block_table, int page_size, int table_cols, void* out, const int* positions,
                            const int* seq_ids, const float* slopes, int B, int H, int G, int D, int Dv, float scale,
                            int window, int keep_first, int impl, void* stream);
+/* The same kernels with a chunk mask (chunk > 0: floor(i / chunk) == floor(j / chunk) as well), a per-head sink logit in
+ * the softmax denominator (sinks [H] fp32 or NULL) and explicit cache-row pitches (k_row, v_row, in elements: v_row ==
+ * k_row when the values are columns of the key rows).  nxd_qk_prep_cache_write adds norm weights (fp32 [D] or NULL),
+ * pairwise rotation from cos / sin tables [positions, rope_dims / 2] and value_from_key (cached value = raw key). */
+int nxd_qk_prep_cache_write(int dtype, const void* qkv, long long ld, void* q_out, void* cache_k, void* cache_v,
+                            long long k_stride_line, long long k_stride_head, long long v_stride_line,
+                            long long v_stride_head, const int* block_table, int page_size, int table_cols,
+                            const int* q_start, const int* n_new, const int* seq_ids, int B, int Tn, int H, int G, int D,
+                            int Dv, int has_kv, int normalize, float eps, int max_pos, int writeback,
+                            const float* q_weight, const float* k_weight, const float* rope_cos, const float* rope_sin,
+                            int rope_dims, int value_from_key, void* stream);
+int nxd_masked_attn_prefill(int dtype, const void* q, const void* cache_k, const void* cache_v, long long k_stride_line,
+                            long long k_stride_head, long long k_row, long long v_stride_line, long long v_stride_head,
+                            long long v_row, const int* block_table, int page_size, int table_cols, void* out,
+                            const int* q_start, const int* n_new, const int* seq_ids, const float* slopes,
+                            const float* sinks, int B, int Tn, int H, int G, int D, int Dv, float scale, int window,
+                            int keep_first, int chunk, int impl, void* stream);
+int nxd_masked_attn_decode(int dtype, const void* q, const void* cache_k, const void* cache_v, long long k_stride_line,
+                           long long k_stride_head, long long k_row, long long v_stride_line, long long v_stride_head,
+                           long long v_row, const int* block_table, int page_size, int table_cols, void* out,
+                           const int* positions, const int* seq_ids, const float* slopes, const float* sinks, int B, int H,
+                           int G, int D, int Dv, float scale, int window, int keep_first, int chunk, int impl,
+                           void* stream);
+/* latent attention: un-rotated query columns -> q_nope, rotated query columns -> q_rot, cache row [norm(c) * w | k_rot] */
+int nxd_latent_prep(int dtype, const void* proj, long long ld, int q_off, int kv_off, void* q_nope, long long nope_head,
+                    void* q_rot, long long rot_head, void* cache, long long stride_line, long long row_pitch,
+                    const int* block_table, int page_size, int table_cols, const float* c_weight, const float* rope_cos,
+                    const float* rope_sin, const int* q_start, const int* n_new, const int* seq_ids, int B, int Tn, int H,
+                    int dim, int rot, int rank, float eps, int max_pos, void* stream);
+/* recurrent matrix memory: fp32 gates (soft cap, log-sigmoid forget gate), scan over a step on the line's fp32 state,
+ * gated / normalised head output, squared ReLU */
+int nxd_mlstm_gates(int dtype, const void* h, const void* w, const float* bias, float* gi, float* gf, long long N, int W,
+                    int H, float cap, void* stream);
+int nxd_mlstm_scan(int dtype, const void* proj, long long ld, int q_off, int k_off, int v_off, const float* gi,
+                   const float* gf, float* state_s, float* state_n, float* state_m, float* next_n, float* next_m,
+                   float* out, const int* q_start, const int* n_new, const int* seq_ids, int B, int Tn, int H, int D,
+                   int Dv, float qscale, void* stream);
+int nxd_head_norm_gate(int o_dtype, int dtype, const void* o, const void* gate, long long ld_g, int g_off,
+                       const float* weight, void* out, long long N, int H, int Dv, int normalize, float eps, void* stream);
+int nxd_relu_squared(int dtype, const void* x, void* y, long long n, void* stream);
+/* x (fp32, in place) += norm(y) * w_post (y may be NULL); h (may be NULL) = cast(norm(x) * w_next); center: 1 = layer
+ * norm without bias, 0 = RMS norm */
+int nxd_norm_chain(int y_dtype, int h_dtype, const void* y, const float* w_post, float* x, const float* w_next, void* h,
+                   long long rows, int W, float eps, int center, void* stream);
 /* tcgen05 flash attention with window / kept first keys / distance bias; tensors and strides as nxd_flash_attn_fwd_tc */
 int nxd_flash_attn_fwd_tc_window(const void* q, const void* k, const void* v, void* o, const long long* strides, int B,
                                  int Hq, int Hkv, int Sq, int Sk, int D, float scale, int window, int keep_first,

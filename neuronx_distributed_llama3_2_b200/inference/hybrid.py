@@ -1,0 +1,173 @@
+"""Rasodra over the framework's step function: chunked attention, latent attention and the recurrent matrix memory on
+one KV cache / state manager.
+
+The step function (``forward_infer``: padding, cache lines through ``seq_ids``, indexed logits, sampler, ``generate``),
+the schedulers and the runners are the mixin's; this class says what a layer does with the stream:
+
+  * ``hidden`` is the fp32 residual stream ``x``, ``residual`` carries ``norm1(x)`` of the layer about to run, in the
+    activation dtype: the norm after a sublayer, the residual add and the norm before the next sublayer are one kernel
+    (``ops.norm.norm_chain_``);
+  * ``attention``: q | k projection -> per-head norm + rotation + cache write (K = normalised rotated key, V = the key as
+    projected) -> attention over the cache with the chunk mask -> output projection;
+  * ``latent_attention``: q | latent | gate projection -> latent norm, rotations and the cache row ``[c | k_rot]`` ->
+    absorbed queries (one batched product with ``uk``) -> attention over the latent rows with the sink in the
+    denominator (one key/value "head", value = the ``c`` columns of the same tensor) -> per-head ``uv`` product ->
+    sigmoid gate -> output projection;
+  * ``mlstm``: q | k | v | gate projection, fp32 gate dot products -> scan over the step's tokens on the line's fp32 state
+    -> unit-RMS per head, weight, sigmoid gate -> output projection;
+  * a layer with ``weights_of`` runs its owner's modules on cache tensors / state of its own (the cache and the state are
+    indexed by the position in the layer list, the modules by the owner).
+A step may start at any position: attention reads earlier keys from the cache, the scan continues from the line's state.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from ..models.rasodra import RasodraConfig, RasodraForCausalLM
+from ..ops import activation as act_ops
+from ..ops import latent_attention as la_ops
+from ..ops import mlstm as mlstm_ops
+from ..ops import rope as rope_ops
+from ..ops import window_attention as wa_ops
+from .config import InferenceConfig
+from .kv_cache import KVCache
+from .model import KVCacheInferenceMixin
+
+
+class RasodraInferenceModel(KVCacheInferenceMixin, RasodraForCausalLM):
+    supports_prefill_at_offset = True
+
+    def __init__(self, config: RasodraConfig, inference_config: Optional[InferenceConfig] = None, device=None):
+        RasodraForCausalLM.__init__(self, config, device=device)
+        self._init_inference(inference_config)
+        self._sequence = self.layer_sequence()
+        self._rope_cache: Dict[Tuple[int, float], Tuple[torch.Tensor, torch.Tensor]] = {}
+        self.layer_probe = None            # callable(i, x) after every layer run (debugging / layer-by-layer checks)
+
+    # -- where the pieces are ---------------------------------------------------------------------------------------
+    def _decoder_layers(self):
+        return self._sequence
+
+    def _embedding(self):
+        return self.embed_tokens
+
+    def _final_norm(self):
+        return self.norm
+
+    def init_kv_cache(self, device=None, dtype=None) -> KVCache:
+        ic, cfg = self.inference_config, self.config
+        device = device or next(self.parameters()).device
+        specs, states = [], {}
+        for i, L in enumerate(cfg.layers):
+            m = L.mixer
+            if L.type == "attention":
+                specs.append((m.kv_heads, m.dim, m.vdim))
+            elif L.type == "latent_attention":
+                specs.append((1, m.kv_rank + m.rot_dim, m.kv_rank, "columns"))
+            else:
+                specs.append(None)
+                states[i] = {"S": (m.heads, m.dim, m.vdim), "n": (m.heads, m.dim), "m": (m.heads,)}
+        self.kv_cache = KVCache(len(cfg.layers), ic.max_batch_size, 0, ic.seq_len, 0, dtype=dtype or cfg.torch_dtype,
+                                device=device, paged=ic.paged_kv, page_size=ic.page_size,
+                                num_pages=ic.num_kv_pages if ic.paged_kv else None, layer_specs=specs, state_specs=states)
+        return self.kv_cache
+
+    def _rotary_tables(self, rot, device) -> Tuple[torch.Tensor, torch.Tensor]:
+        key = (rot.dims, rot.base)
+        t = self._rope_cache.get(key)
+        if t is None or t[0].device != device or t[0].shape[0] < self.kv_cache.seq_len:
+            t = rope_ops.build_interleaved_rope_cache(self.kv_cache.seq_len, rot.dims, rot.base, device=device)
+            self._rope_cache[key] = t
+        return t
+
+    def _embed(self, input_ids: torch.Tensor) -> torch.Tensor:
+        return super()._embed(input_ids).float()           # the stream is fp32 from the first layer on
+
+    def _add_norm(self, norm, hidden: torch.Tensor, residual: Optional[torch.Tensor]):
+        """Only the model's final norm comes through here: plain norm of the fp32 stream."""
+        return norm(hidden, out_dtype=self.config.torch_dtype), None
+
+    # -- mixers: h [B, T, W] in the activation dtype -> [B, T, W] ---------------------------------------------------------
+    def _paged(self) -> dict:
+        kc = self.kv_cache
+        return dict(block_table=kc.block_table, page_size=kc.page_size) if kc.paged else {}
+
+    def _mix_attention(self, i, mixer, h, q_start, n_new, seq_ids):
+        m, cfg = mixer.cfg, self.config
+        B, T, _ = h.shape
+        ck, cv = self.kv_cache.layer(i)
+        paged = self._paged()
+        qk = mixer.qk_proj(h)
+        rope = self._rotary_tables(m.rot, h.device) if m.rot is not None else None
+        q = wa_ops.qk_norm_cache_write(qk, ck, cv, q_start, m.heads, m.kv_heads, m.dim, m.vdim, cfg.rms_norm_eps,
+                                       n_new=n_new, seq_ids=seq_ids, q_weight=mixer.q_norm, k_weight=mixer.k_norm,
+                                       rope=rope, value_from_key=True, **paged)
+        if T == 1:
+            o = wa_ops.window_attention_decode(q[:, 0], ck, cv, q_start, m.scale, seq_ids=seq_ids, chunk=m.chunk, **paged)
+        else:
+            o = wa_ops.window_attention_prefill(q, ck, cv, q_start, m.scale, n_new=n_new, seq_ids=seq_ids, chunk=m.chunk,
+                                                **paged)
+        return mixer.o_proj(o.reshape(B, T, m.heads * m.vdim))
+
+    def _mix_latent(self, i, mixer, h, q_start, n_new, seq_ids):
+        m, cfg, dt = mixer.cfg, self.config, self.config.torch_dtype
+        B, T, _ = h.shape
+        N, H, R = B * T, m.heads, m.kv_rank
+        ck, cv = self.kv_cache.layer(i)                    # cv: the first kv_rank columns of ck's rows
+        paged = self._paged()
+        proj = mixer.in_proj(h)
+        q_abs = torch.empty(N, H, R + m.rot_dim, dtype=dt, device=h.device)
+        q_nope = la_ops.latent_prep(proj, 0, mixer.q_cols, q_abs, ck, mixer.kv_norm, self._rotary_tables(m.rot, h.device),
+                                    q_start, H, m.dim, m.rot_dim, R, cfg.rms_norm_eps, n_new=n_new, seq_ids=seq_ids,
+                                    **paged)
+        # absorption: W_uk_h^T q_nope_h for every head in one batched product
+        q_abs[..., :R] = torch.bmm(q_nope.transpose(0, 1), mixer.uk).transpose(0, 1)
+        if T == 1:
+            o_lat = wa_ops.window_attention_decode(q_abs, ck, cv, q_start, m.scale, seq_ids=seq_ids, sinks=mixer.sink,
+                                                   **paged)
+        else:
+            o_lat = wa_ops.window_attention_prefill(q_abs.reshape(B, T, H, R + m.rot_dim), ck, cv, q_start, m.scale,
+                                                    n_new=n_new, seq_ids=seq_ids, sinks=mixer.sink, **paged)
+        o = torch.bmm(o_lat.reshape(N, H, R).transpose(0, 1), mixer.uv_t).transpose(0, 1).contiguous()   # [N, H, vdim]
+        y = mlstm_ops.head_norm_gate(o, proj.reshape(N, -1), mixer.q_cols + mixer.kv_cols, H, m.vdim, None,
+                                     cfg.rms_norm_eps, False, dt)
+        return mixer.o_proj(y.reshape(B, T, H * m.vdim))
+
+    def _mix_mlstm(self, i, mixer, h, q_start, n_new, seq_ids):
+        m, cfg, dt = mixer.cfg, self.config, self.config.torch_dtype
+        B, T, W = h.shape
+        N, H = B * T, m.heads
+        st = self.kv_cache.state(i)
+        proj = mixer.in_proj(h)
+        gi, gf = mlstm_ops.mlstm_gates(h.reshape(N, W), mixer.gate_weight, mixer.gate_bias, H, m.gate_cap)
+        o = mlstm_ops.mlstm_scan(proj, (0, H * m.dim, 2 * H * m.dim), gi, gf, (st["S"], st["n"], st["m"]), q_start, H,
+                                 m.dim, m.vdim, m.dim ** -0.5, n_new=n_new, seq_ids=seq_ids)
+        y = mlstm_ops.head_norm_gate(o.reshape(N, H, m.vdim), proj.reshape(N, -1), 2 * H * m.dim + H * m.vdim, H, m.vdim,
+                                     mixer.out_norm, cfg.rms_norm_eps, True, dt)
+        return mixer.o_proj(y.reshape(B, T, H * m.vdim))
+
+    _MIX = {"attention": _mix_attention, "latent_attention": _mix_latent, "mlstm": _mix_mlstm}
+
+    # -- one layer --------------------------------------------------------------------------------------------------
+    def _layer(self, i: int, layer, hidden, residual, positions, seq_ids, lengths, prefill):
+        dt = self.config.torch_dtype
+        x = hidden if hidden.is_contiguous() else hidden.contiguous()
+        h = residual if residual is not None else layer.norm1(x, out_dtype=dt)
+        q_start = positions[:, 0]
+        n_new = self._step_new_tokens if prefill else None
+        y = self._MIX[layer.type](self, i, layer.mixer, h, q_start, n_new, seq_ids)
+        nxt = self._sequence[i + 1].norm1 if i + 1 < len(self._sequence) else None
+        if layer.mlp is None:
+            x, h = layer.norm1b.add_to(x, y, nxt, dt)
+        else:
+            x, h = layer.norm1b.add_to(x, y, layer.norm2, dt)
+            y = layer.mlp.down_proj(act_ops.relu_squared(layer.mlp.up_proj(h)))
+            x, h = layer.norm2b.add_to(x, y, nxt, dt)
+        if self.layer_probe is not None:
+            self.layer_probe(i, x)
+        return x, h
+
+    def forward_speculation(self, *a, **kw):
+        raise NotImplementedError("the speculation verify graph is not wired for this family")

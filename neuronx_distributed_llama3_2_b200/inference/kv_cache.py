@@ -14,6 +14,13 @@ graphs that captured it see the new mapping.
 Layers need not be alike: ``layer_specs[i] = (kv_heads, key_dim, value_dim)`` gives layer ``i`` its own shapes (key and
 value sizes may differ), and ``share_from[i] = j`` makes layer ``i`` read layer ``j``'s keys and values instead of
 holding its own (cross-layer KV sharing: ``layer(i)`` returns ``j``'s tensors, nothing is allocated for ``i``).
+A spec ``(kv_heads, key_dim, value_dim, "columns")`` keeps ONE tensor per layer whose value is the first ``value_dim``
+columns of the key rows (the latent cache of a compressed key/value projection); a spec ``None`` is a layer without
+keys and values.
+
+Recurrent layers keep a STATE per cache line instead: ``state_specs[i] = {name: shape}`` allocates fp32 tensors
+``[lines, *shape]`` (``state(i)``).  State is per line, not per page: ``fork`` copies it, and a layer that starts a
+sequence at position 0 starts from zero by itself, so a line that is handed out again needs no clearing.
 """
 from __future__ import annotations
 
@@ -26,7 +33,8 @@ class KVCache:
     def __init__(self, num_layers: int, lines: int, kv_heads: int, seq_len: int, head_dim: int,
                  dtype: torch.dtype = torch.bfloat16, device=None, paged: bool = False, page_size: int = 128,
                  num_pages: Optional[int] = None, layer_specs: Optional[List[Optional[Tuple[int, int, int]]]] = None,
-                 share_from: Optional[Dict[int, int]] = None):
+                 share_from: Optional[Dict[int, int]] = None,
+                 state_specs: Optional[Dict[int, Dict[str, Tuple[int, ...]]]] = None):
         self.num_layers, self.lines, self.kv_heads, self.seq_len, self.head_dim = num_layers, lines, kv_heads, seq_len, head_dim
         self.share_from = dict(share_from or {})
         for i, j in self.share_from.items():
@@ -58,9 +66,19 @@ class KVCache:
                 self.k.append(None)
                 self.v.append(None)
                 continue
-            g, dk, dv = specs[i]
+            if specs[i] is None:                       # a layer without keys and values (recurrent state only)
+                self.k.append(None)
+                self.v.append(None)
+                continue
+            g, dk, dv = specs[i][:3]
             self.k.append(torch.zeros((lead, g, rows, dk), dtype=dtype, device=device))
-            self.v.append(torch.zeros((lead, g, rows, dv), dtype=dtype, device=device))
+            if len(specs[i]) > 3 and specs[i][3] == "columns":
+                self.v.append(self.k[-1][..., :dv])    # the values are columns of the key rows: one tensor
+            else:
+                self.v.append(torch.zeros((lead, g, rows, dv), dtype=dtype, device=device))
+        self.states: Dict[int, Dict[str, torch.Tensor]] = {
+            i: {name: torch.zeros((lines,) + tuple(shape), dtype=torch.float32, device=device)
+                for name, shape in spec.items()} for i, spec in (state_specs or {}).items()}
 
     def owns(self, i: int) -> bool:
         """False for a layer that reads another layer's keys and values."""
@@ -70,11 +88,23 @@ class KVCache:
         i = self.share_from.get(i, i)
         return self.k[i], self.v[i]
 
+    def state(self, i: int) -> Dict[str, torch.Tensor]:
+        """The recurrent state tensors ``[lines, ...]`` (fp32) of layer ``i``."""
+        return self.states[i]
+
     def _tensors(self) -> List[torch.Tensor]:
-        return [t for t in self.k + self.v if t is not None]
+        """Every allocation once (a value tensor that is a column range of its key tensor is not one)."""
+        out = []
+        for t in self.k + self.v:
+            if t is not None and t._base is None:
+                out.append(t)
+        return out
+
+    def _state_tensors(self) -> List[torch.Tensor]:
+        return [t for d in self.states.values() for t in d.values()]
 
     def reset(self) -> None:
-        for t in self._tensors():
+        for t in self._tensors() + self._state_tensors():
             t.zero_()
         if self.pool is not None:
             for line in range(self.lines):
@@ -116,6 +146,8 @@ class KVCache:
         copy = self.pool.fork(src, dst)
         if copy is not None:
             self._copy_page(*copy)
+        for t in self._state_tensors():
+            t[dst].copy_(t[src])
         self.sync_lines([dst])
 
     def prepare_write(self, line: int, pos: int) -> None:
@@ -128,4 +160,4 @@ class KVCache:
             self.sync_lines([line])
 
     def bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self._tensors())
+        return sum(t.numel() * t.element_size() for t in self._tensors() + self._state_tensors())

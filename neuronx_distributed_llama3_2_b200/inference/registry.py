@@ -88,9 +88,29 @@ def _gekazen_cls():
     return GekazenInferenceModel
 
 
+def _rasodra_config(d, dtype):
+    from ..models.rasodra import RasodraConfig
+
+    return RasodraConfig.from_dict(d, torch_dtype=dtype)
+
+
+def _rasodra_convert(sd, cfg):
+    from ..models.rasodra import convert_rasodra_state_dict
+
+    return convert_rasodra_state_dict(sd, cfg)
+
+
+def _rasodra_cls():
+    from .hybrid import RasodraInferenceModel
+
+    return RasodraInferenceModel
+
+
 register_family(ModelFamily("llama", lambda c: _arch(c).startswith("llama"), _llama_config, _llama_cls, _llama_convert))
 register_family(ModelFamily("gekazen", lambda c: _arch(c) == "gekazen", _gekazen_config, _gekazen_cls, _gekazen_convert,
                             kernel_group="window_moe_serving"))
+register_family(ModelFamily("rasodra", lambda c: _arch(c) == "rasodra", _rasodra_config, _rasodra_cls, _rasodra_convert,
+                            kernel_group="hybrid_serving"))
 
 
 def read_config(model_dir: str) -> Dict[str, Any]:

@@ -352,3 +352,13 @@ class GekazenRunner(InferenceRunner):
 
         kw.setdefault("model_cls", GekazenInferenceModel)
         super().__init__(*a, **kw)
+
+
+class RasodraRunner(InferenceRunner):
+    """Runner of the Rasodra family (``models/rasodra.py``): same buckets, graphs and generate loop."""
+
+    def __init__(self, *a, **kw):
+        from .hybrid import RasodraInferenceModel
+
+        kw.setdefault("model_cls", RasodraInferenceModel)
+        super().__init__(*a, **kw)

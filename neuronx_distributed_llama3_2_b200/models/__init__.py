@@ -7,3 +7,5 @@ from .gpt_neox import GPTNeoXConfig, GPTNeoXForCausalLM, codegen25_7b, gpt_neox_
 from .bert import BertConfig, BertForPreTraining, bert_large, convert_bert_hf_state_dict, tiny_bert  # noqa: F401
 from .dbrx import DbrxConfig, DbrxForCausalLM, convert_dbrx_hf_state_dict, dbrx_instruct, tiny_dbrx  # noqa: F401
 from .gekazen import GekazenConfig, GekazenForCausalLM, convert_gekazen_state_dict, tiny_gekazen  # noqa: F401
+from .rasodra import (RasodraConfig, RasodraForCausalLM, convert_rasodra_state_dict, export_rasodra_state_dict,  # noqa: F401
+                      tiny_rasodra)

@@ -49,6 +49,14 @@ GROUPS = {
 GROUPS["window_moe_serving"] = GROUPS["window_moe"] + [
     "gemm_tcgen05.cu", "gemm_smallm.cu", "fused_gemm_ar.cu", "tma_host.cu", "flash_attn_tc.cu", "attn_tc_host.cu"]
 
+# the hybrid families (chunked / latent attention, recurrent matrix memory, dense feed-forward): the attention-over-cache
+# kernels, the norm kernels, their own two sources and the GEMM kernels behind the linear layers
+GROUPS["hybrid_serving"] = ["window_attention.cu", "post_norm.cu", "latent_attention.cu", "mlstm.cu", "runtime.cu",
+                            "gemm_tcgen05.cu", "gemm_smallm.cu", "fused_gemm_ar.cu", "tma_host.cu"]
+
+# sources whose fp32 state is carried over thousands of steps: no approximate exp / tanh / division
+PRECISE_SOURCES = {"mlstm.cu"}
+
 _lib: Optional[ctypes.CDLL] = None
 _group_libs = {}
 _preferred_group: Optional[str] = None
@@ -130,7 +138,8 @@ def build(force: bool = False, verbose: bool = False, group: Optional[str] = Non
         if (not force and os.path.exists(obj) and os.path.getmtime(obj) > os.path.getmtime(src)
                 and os.path.getmtime(obj) > hdr_time):
             return obj
-        cmd = [nvcc] + NVCC_FLAGS + ["-I", INCLUDE_DIR, "-I", CSRC_DIR, "-c", src, "-o", obj]
+        flags = [f for f in NVCC_FLAGS if not (f == "--use_fast_math" and os.path.basename(src) in PRECISE_SOURCES)]
+        cmd = [nvcc] + flags + ["-I", INCLUDE_DIR, "-I", CSRC_DIR, "-c", src, "-o", obj]
         res = subprocess.run(cmd, capture_output=True, text=True)
         logs[src] = res.stderr
         if res.returncode != 0:

@@ -1,4 +1,4 @@
-"""SwiGLU on the fused gate|up tensor."""
+"""Feed-forward activations: SwiGLU on the fused gate|up tensor, squared ReLU."""
 from __future__ import annotations
 
 import ctypes as _c
@@ -49,3 +49,15 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     if gate_up.is_cuda and gate_up.dtype == torch.bfloat16 and I % 8 == 0 and _lib.available():
         return _SwiGLUFn.apply(gate_up)
     return swiglu_ref(gate_up)
+
+
+def relu_squared(x: torch.Tensor) -> torch.Tensor:
+    """``max(x, 0) ** 2`` (the activation of a two-matrix feed-forward)."""
+    if x.is_cuda and x.dtype in (torch.bfloat16, torch.float32) and x.is_contiguous() and _lib.available("hybrid_serving"):
+        out = torch.empty_like(x)
+        L = _lib.lib("hybrid_serving")
+        rc = L.nxd_relu_squared(_c.c_int(0 if x.dtype == torch.bfloat16 else 1), _lib.ptr(x), _lib.ptr(out),
+                                _c.c_longlong(x.numel()), _lib.stream_ptr())
+        _lib.check(rc, "nxd_relu_squared", L)
+        return out
+    return F.relu(x).square()

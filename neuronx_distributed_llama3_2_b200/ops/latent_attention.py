@@ -1,0 +1,79 @@
+"""Latent (compressed key/value) attention: the step's work on the fused projection output before the attention kernel
+(``csrc/latent_attention.cu``).
+
+The projection row of a token holds ``heads`` query heads laid out ``[dim un-rotated | rot rotated]`` and ``rank``
+compressed key/value columns followed by ``rot`` columns of one rotated key part shared by all heads.  The cache keeps
+one row per token, ``[c | k_rot]`` with ``c = rms_norm(compressed) * weight``.  Because
+
+    score_h(i, j) = <q_nope_h, W_uk_h c_j> + <q_rot_h, k_rot_j> = <[W_uk_h^T q_nope_h | q_rot_h], [c_j | k_rot_j]>
+
+all heads attend to the same rows with an absorbed query (``ops.window_attention`` with one key/value head whose value
+is the ``c`` part of the row), and the per-head value projection follows the attention.
+"""
+from __future__ import annotations
+
+import ctypes as _c
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from .rope import rope_interleaved_ref
+
+GROUP = "hybrid_serving"
+
+
+def _i32(t):
+    if t is None:
+        return None
+    return t if (t.dtype == torch.int32 and t.is_contiguous()) else t.to(torch.int32).contiguous()
+
+
+def latent_prep(proj: torch.Tensor, q_off: int, kv_off: int, q_abs: torch.Tensor, cache: torch.Tensor,
+                c_weight: torch.Tensor, rope: Tuple[torch.Tensor, torch.Tensor], q_start: torch.Tensor, heads: int,
+                dim: int, rot: int, rank: int, eps: float, n_new: Optional[torch.Tensor] = None,
+                seq_ids: Optional[torch.Tensor] = None, block_table: Optional[torch.Tensor] = None,
+                page_size: int = 0) -> torch.Tensor:
+    """``proj [B, T, ld]``.  Returns ``q_nope [B*T, heads, dim]`` (the un-rotated query columns, for the absorption
+    product) and fills ``q_abs[..., rank:]`` (``q_abs [B*T, heads, rank + rot]``) with the rotated query part; writes the
+    cache row ``[c | k_rot]`` of every real token at (line, position).  ``cache [lines | pages, 1, rows, rank + rot]``."""
+    B, T, ld = proj.shape
+    N = B * T
+    cos, sin = rope
+    q_nope = torch.empty(N, heads, dim, dtype=proj.dtype, device=proj.device)
+    if proj.is_cuda and proj.dtype in (torch.bfloat16, torch.float32) and _lib.available(GROUP):
+        assert proj.is_contiguous() and q_abs.is_contiguous() and cache.stride(3) == 1
+        bt = _i32(block_table)
+        max_pos = bt.shape[1] * page_size if bt is not None else cache.shape[2]
+        L = _lib.lib(GROUP)
+        es = proj.element_size()
+        rc = L.nxd_latent_prep(_c.c_int({torch.bfloat16: 0, torch.float32: 1}[proj.dtype]), _lib.ptr(proj),
+                               _c.c_longlong(ld), _c.c_int(q_off), _c.c_int(kv_off), _lib.ptr(q_nope), _c.c_longlong(dim),
+                               _c.c_void_p(q_abs.data_ptr() + rank * es), _c.c_longlong(rank + rot), _lib.ptr(cache),
+                               _c.c_longlong(cache.stride(0)), _c.c_longlong(cache.stride(2)), _lib.ptr(bt),
+                               _c.c_int(page_size if bt is not None else 0), _c.c_int(bt.shape[1] if bt is not None else 0),
+                               _lib.ptr(c_weight), _lib.ptr(cos), _lib.ptr(sin), _lib.ptr(_i32(q_start)),
+                               _lib.ptr(_i32(n_new)), _lib.ptr(_i32(seq_ids)), _c.c_int(B), _c.c_int(T), _c.c_int(heads),
+                               _c.c_int(dim), _c.c_int(rot), _c.c_int(rank), _c.c_float(eps), _c.c_int(max_pos),
+                               _lib.stream_ptr())
+        _lib.check(rc, "nxd_latent_prep", L)
+        return q_nope
+    pos = q_start.long().reshape(B, 1) + torch.arange(T, device=proj.device).reshape(1, T)
+    q = proj[..., q_off: q_off + heads * (dim + rot)].reshape(B, T, heads, dim + rot)
+    q_nope.copy_(q[..., :dim].reshape(N, heads, dim))
+    q_abs[..., rank:] = rope_interleaved_ref(q[..., dim:].float(), pos, cos, sin).to(proj.dtype).reshape(N, heads, rot)
+    kv = proj[..., kv_off: kv_off + rank + rot].float()
+    c = kv[..., :rank]
+    c = c / torch.sqrt(c.pow(2).mean(-1, keepdim=True) + eps) * c_weight.float()
+    kr = rope_interleaved_ref(kv[..., rank:].unsqueeze(-2), pos, cos, sin).squeeze(-2)
+    rows = torch.cat([c, kr], dim=-1).to(cache.dtype)
+    for b in range(B):
+        cnt = T if n_new is None else min(int(n_new[b]), T)
+        line = b if seq_ids is None else int(seq_ids[b])
+        for t in range(cnt):
+            p = int(q_start[b]) + t
+            if block_table is not None:
+                cache[int(block_table[line, p // page_size]), 0, p % page_size] = rows[b, t]
+            else:
+                cache[line, 0, p] = rows[b, t]
+    return q_nope

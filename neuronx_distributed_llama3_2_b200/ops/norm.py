@@ -2,7 +2,7 @@
 from __future__ import annotations
 
 import ctypes as _c
-from typing import Tuple
+from typing import Optional, Tuple
 
 import torch
 
@@ -137,3 +137,37 @@ def rms_norm_offset(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: tor
         return h
     xf = x.float()
     return (xf / torch.sqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * (offset + w.float())).to(out_dtype)
+
+
+# ---- pre- and post-norm of a sublayer boundary in one pass over an fp32 stream (``csrc/post_norm.cu``) ---------------
+def norm_ref(v: torch.Tensor, w: torch.Tensor, eps: float, center: bool) -> torch.Tensor:
+    vf = v.float()
+    if center:
+        vf = vf - vf.mean(-1, keepdim=True)
+    return vf / torch.sqrt(vf.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+
+
+def norm_chain_(x: torch.Tensor, y: Optional[torch.Tensor], w_post: Optional[torch.Tensor],
+                w_next: Optional[torch.Tensor], eps: float, out_dtype: Optional[torch.dtype] = None,
+                center: bool = True):
+    """``x += norm(y) * w_post`` in place on the fp32 stream ``x`` (skipped without ``y``), then
+    ``h = (norm(x) * w_next).to(out_dtype)`` (skipped without ``w_next``); returns ``(x, h)``.  ``center``: layer norm
+    without bias (mean removed, variance of the deviations); otherwise RMS norm.  Weights are plain (not one-plus)."""
+    assert x.dtype == torch.float32 and (y is None or y.shape == x.shape)
+    W = x.shape[-1]
+    if x.is_cuda and (y is None or y.dtype in (torch.bfloat16, torch.float32)) and _lib.available("hybrid_serving"):
+        assert x.is_contiguous()
+        y2 = None if y is None else (y if y.is_contiguous() else y.contiguous())
+        wp = None if w_post is None else w_post.float().contiguous()
+        wn = None if w_next is None else w_next.float().contiguous()
+        h = torch.empty(x.shape, dtype=out_dtype, device=x.device) if wn is not None else None
+        L = _lib.lib("hybrid_serving")
+        rc = L.nxd_norm_chain(_c.c_int(_post_code(y2.dtype) if y2 is not None else 1),
+                              _c.c_int(_post_code(out_dtype) if h is not None else 1), _lib.ptr(y2), _lib.ptr(wp),
+                              _lib.ptr(x), _lib.ptr(wn), _lib.ptr(h), _c.c_longlong(x.numel() // W), _c.c_int(W),
+                              _c.c_float(eps), _c.c_int(int(center)), _lib.stream_ptr())
+        _lib.check(rc, "nxd_norm_chain", L)
+        return x, h
+    if y is not None:
+        x.add_(norm_ref(y, w_post, eps, center))
+    return x, (norm_ref(x, w_next, eps, center).to(out_dtype) if w_next is not None else None)

@@ -42,6 +42,28 @@ def build_rope_cache(max_pos: int, head_dim: int, theta: float = 500000.0, rope_
     return freqs.cos().contiguous(), freqs.sin().contiguous()
 
 
+def build_interleaved_rope_cache(max_pos: int, dims: int, base: float, device=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """fp32 ``cos`` / ``sin`` tables ``[max_pos, dims/2]`` of the angles ``p * base ** (-2 i / dims)``, evaluated in
+    float64 (a position of a few thousand times a frequency loses digits of the angle in fp32)."""
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    ang = torch.outer(torch.arange(max_pos, dtype=torch.float64), torch.pow(torch.tensor(float(base), dtype=torch.float64),
+                                                                             -2.0 * i / dims))
+    return ang.cos().float().contiguous().to(device), ang.sin().float().contiguous().to(device)
+
+
+def rope_interleaved_ref(x: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """``x [..., heads, D]`` with ``positions [...]``: the pairs ``(2i, 2i + 1)`` of the first ``2 * cos.shape[1]``
+    dimensions turn by the angle of (position, i): ``(u, v) -> (u cos - v sin, v cos + u sin)``; the rest pass."""
+    rot = 2 * cos.shape[1]
+    c = cos[positions.long()].unsqueeze(-2).to(x.dtype)
+    s = sin[positions.long()].unsqueeze(-2).to(x.dtype)
+    u, v = x[..., 0:rot:2], x[..., 1:rot:2]
+    out = x.clone()
+    out[..., 0:rot:2] = u * c - v * s
+    out[..., 1:rot:2] = v * c + u * s
+    return out
+
+
 def _positions(T: int, pos_div: int, pos_mod: int, positions, device):
     if positions is not None:
         return positions.reshape(-1).long()

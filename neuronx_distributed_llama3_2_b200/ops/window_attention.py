@@ -2,7 +2,12 @@
 (``csrc/window_attention.cu``), next to the plain causal ops of ``ops/attention.py``.
 
     visible(i, j) = j <= i and (window is None or i - j < window or j < keep_first)
+                    and (chunk is None or i // chunk == j // chunk)        chunk boundaries at absolute multiples of the size
     score(i, j)   = scale * <q_i, k_j> - slope_h * (i - j)
+    p(i, j)       = exp(score(i, j)) / (sum over visible j' of exp(score(i, j')) [+ exp(sink_h)])
+
+``sinks``: a learned per-head logit that is attached to no position and only takes probability mass.  The value rows may be
+a column range of the key rows (``cache_v`` a view of ``cache_k``): the cache of a compressed key/value projection.
 
 Head sizes are free (query/key size ``D`` and value size ``Dv`` may differ); activations and cache are bf16 or fp32, the
 softmax and the unit-RMS normalisation of queries and keys run in fp32.  The prefill op reads keys and values from the
@@ -51,26 +56,43 @@ def _cache_rows(cache: torch.Tensor, line: int, n: int, block_table, page_size: 
     return cache[pages].permute(1, 0, 2, 3).reshape(cache.shape[1], -1, cache.shape[3])[:, :n]
 
 
-def _cache_args(cache_k, cache_v, block_table, page_size):
+def _cache_args(cache_k, cache_v, block_table, page_size, rows: bool = False):
+    """Strides (in elements) of the cache tensors; with ``rows`` also the pitch between consecutive cache rows, which
+    lets ``cache_v`` be a column range of ``cache_k``."""
     bt = _i32(block_table)
-    return (_c.c_longlong(cache_k.stride(0)), _c.c_longlong(cache_k.stride(1)), _c.c_longlong(cache_v.stride(0)),
-            _c.c_longlong(cache_v.stride(1)), _lib.ptr(bt), _c.c_int(page_size if bt is not None else 0),
-            _c.c_int(bt.shape[1] if bt is not None else 0)), bt
+    assert cache_k.stride(3) == 1 and cache_v.stride(3) == 1
+    k = (_c.c_longlong(cache_k.stride(0)), _c.c_longlong(cache_k.stride(1)))
+    v = (_c.c_longlong(cache_v.stride(0)), _c.c_longlong(cache_v.stride(1)))
+    if rows:
+        k, v = k + (_c.c_longlong(cache_k.stride(2)),), v + (_c.c_longlong(cache_v.stride(2)),)
+    else:
+        assert cache_k.stride(2) == cache_k.shape[3] and cache_v.stride(2) == cache_v.shape[3]
+    return k + v + (_lib.ptr(bt), _c.c_int(page_size if bt is not None else 0),
+                    _c.c_int(bt.shape[1] if bt is not None else 0)), bt
 
 
 def qk_norm_cache_write(qkv: torch.Tensor, cache_k: Optional[torch.Tensor], cache_v: Optional[torch.Tensor],
                         q_start: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int, eps: float,
                         n_new: Optional[torch.Tensor] = None, seq_ids: Optional[torch.Tensor] = None,
                         normalize: bool = True, block_table: Optional[torch.Tensor] = None,
-                        page_size: int = 0, writeback: bool = False) -> torch.Tensor:
-    """``qkv [B, T, heads*dim (+ kv_heads*dim + kv_heads*vdim)]`` -> ``q [B, T, heads, dim]``; with a cache given the
+                        page_size: int = 0, writeback: bool = False, q_weight: Optional[torch.Tensor] = None,
+                        k_weight: Optional[torch.Tensor] = None, rope: Optional[tuple] = None,
+                        value_from_key: bool = False) -> torch.Tensor:
+    """``q_weight / k_weight [dim]``: weight of the per-head norm (after the division).  ``rope = (cos, sin)`` tables
+    ``[positions, rot/2]`` (``ops.rope.build_interleaved_rope_cache``): queries and keys turn pairwise on their first
+    ``rot`` dimensions, after the norm.  ``value_from_key``: the projection has no value columns, the cached value is
+    the raw key projection (taken ahead of the norm and the rotation).
+
+    ``qkv [B, T, heads*dim (+ kv_heads*dim + kv_heads*vdim)]`` -> ``q [B, T, heads, dim]``; with a cache given the
     key and value heads of the real rows (``t < n_new[b]``) are written at position ``q_start[b] + t`` of cache line
     ``seq_ids[b]``.  ``normalize``: queries and keys are divided by their root mean square over ``dim`` (fp32, ``eps``
     inside the root) before they are written.  ``writeback``: the normalised keys of the real rows also replace the
     raw ones inside ``qkv`` (for a kernel that reads q / k / v as strided views of the projection output)."""
     B, T, n_out = qkv.shape
     has_kv = cache_k is not None
-    assert n_out == heads * dim + (kv_heads * (dim + vdim) if has_kv else 0), (n_out, heads, kv_heads, dim, vdim)
+    n_v = 0 if value_from_key else kv_heads * vdim
+    assert n_out == heads * dim + ((kv_heads * dim + n_v) if has_kv else 0), (n_out, heads, kv_heads, dim, vdim)
+    assert not value_from_key or vdim == dim
     if _use_kernel(qkv):
         assert qkv.is_contiguous() or not writeback
         qkv = qkv if qkv.is_contiguous() else qkv.contiguous()
@@ -81,24 +103,38 @@ def qk_norm_cache_write(qkv: torch.Tensor, cache_k: Optional[torch.Tensor], cach
         cargs, bt = _cache_args(ck, cv, block_table if has_kv else None, page_size)
         max_pos = (bt.shape[1] * page_size if bt is not None else ck.shape[2]) if has_kv else 0
         L = _lib.lib(GROUP)
-        rc = L.nxd_qk_norm_cache_write(_c.c_int(_code(qkv.dtype)), _lib.ptr(qkv), _c.c_longlong(n_out), _lib.ptr(q),
+        qw = q_weight.float().contiguous() if q_weight is not None else None
+        kw = k_weight.float().contiguous() if k_weight is not None else None
+        cos, sin = rope if rope is not None else (None, None)
+        rc = L.nxd_qk_prep_cache_write(_c.c_int(_code(qkv.dtype)), _lib.ptr(qkv), _c.c_longlong(n_out), _lib.ptr(q),
                                        _lib.ptr(ck), _lib.ptr(cv), *cargs, _lib.ptr(qs), _lib.ptr(nn_), _lib.ptr(sid),
                                        _c.c_int(B), _c.c_int(T), _c.c_int(heads), _c.c_int(kv_heads), _c.c_int(dim),
                                        _c.c_int(vdim), _c.c_int(int(has_kv)), _c.c_int(int(normalize)), _c.c_float(eps),
-                                       _c.c_int(max_pos), _c.c_int(int(writeback and has_kv)), _lib.stream_ptr())
-        _lib.check(rc, "nxd_qk_norm_cache_write", L)
+                                       _c.c_int(max_pos), _c.c_int(int(writeback and has_kv)), _lib.ptr(qw), _lib.ptr(kw),
+                                       _lib.ptr(cos), _lib.ptr(sin), _c.c_int(2 * cos.shape[1] if cos is not None else 0),
+                                       _c.c_int(int(value_from_key)), _lib.stream_ptr())
+        _lib.check(rc, "nxd_qk_prep_cache_write", L)
         return q
 
-    def unit(x):
-        if not normalize:
-            return x
-        xf = x.float()
-        return (xf / torch.sqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)
+    pos_bt = q_start.long().reshape(B, 1) + torch.arange(T, device=qkv.device).reshape(1, T)
 
-    q = unit(qkv[..., : heads * dim].reshape(B, T, heads, dim))
+    def unit(x, w):
+        xf = x.float()
+        if normalize:
+            xf = xf / torch.sqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+        if w is not None:
+            xf = xf * w.float()
+        if rope is not None:
+            from .rope import rope_interleaved_ref
+
+            xf = rope_interleaved_ref(xf, pos_bt, rope[0], rope[1])
+        return xf.to(x.dtype)
+
+    q = unit(qkv[..., : heads * dim].reshape(B, T, heads, dim), q_weight)
     if has_kv:
-        k = unit(qkv[..., heads * dim: (heads + kv_heads) * dim].reshape(B, T, kv_heads, dim))
-        v = qkv[..., (heads + kv_heads) * dim:].reshape(B, T, kv_heads, vdim)
+        k_raw = qkv[..., heads * dim: (heads + kv_heads) * dim].reshape(B, T, kv_heads, dim)
+        k = unit(k_raw, k_weight)
+        v = k_raw if value_from_key else qkv[..., (heads + kv_heads) * dim:].reshape(B, T, kv_heads, vdim)
         for b in range(B):
             n = T if n_new is None else int(n_new[b])
             line = b if seq_ids is None else int(seq_ids[b])
@@ -118,7 +154,8 @@ def qk_norm_cache_write(qkv: torch.Tensor, cache_k: Optional[torch.Tensor], cach
 
 
 def window_attention_ref(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_pos: torch.Tensor, scale: float,
-                         window: Optional[int], keep_first: int, slopes: Optional[torch.Tensor]) -> torch.Tensor:
+                         window: Optional[int], keep_first: int, slopes: Optional[torch.Tensor],
+                         chunk: Optional[int] = None, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One sequence in fp32: ``q [Tq, H, D]`` at positions ``q_pos [Tq]`` over keys ``k [G, Tk, D]`` / ``v [G, Tk, Dv]``
     at positions ``0 .. Tk - 1``."""
     H, G = q.shape[1], k.shape[0]
@@ -130,10 +167,17 @@ def window_attention_ref(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_po
     vis = dist >= 0
     if window is not None and window > 0:
         vis = vis & ((dist < window) | (j.reshape(1, -1) < keep_first))
+    if chunk:
+        vis = vis & (torch.div(q_pos.reshape(-1, 1), chunk, rounding_mode="floor")
+                     == torch.div(j.reshape(1, -1), chunk, rounding_mode="floor"))
     if slopes is not None:
         s = s - slopes.float().reshape(H, 1, 1) * dist.float()
     s = s.masked_fill(~vis, float("-inf"))
+    if sinks is not None:
+        s = torch.cat([s, sinks.float().reshape(H, 1, 1).expand(H, s.shape[1], 1)], dim=-1)
     p = torch.softmax(s, dim=-1)
+    if sinks is not None:
+        p = p[..., :-1]
     p = torch.nan_to_num(p, nan=0.0)                                      # a row that sees nothing
     return torch.einsum("hqk,hkd->qhd", p, vf)
 
@@ -142,7 +186,8 @@ def window_attention_prefill(q: torch.Tensor, cache_k: torch.Tensor, cache_v: to
                              scale: float, window: Optional[int] = None, keep_first: int = 0,
                              slopes: Optional[torch.Tensor] = None, n_new: Optional[torch.Tensor] = None,
                              seq_ids: Optional[torch.Tensor] = None, block_table: Optional[torch.Tensor] = None,
-                             page_size: int = 0, impl: str = "auto") -> torch.Tensor:
+                             page_size: int = 0, impl: str = "auto", chunk: Optional[int] = None,
+                             sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``impl``: ``auto`` | ``generic`` (fp32-math tile kernel, any sizes) | ``mma`` (bf16 tensor-core kernel, an error
     where it does not apply) -- for tests and measurements.
 
@@ -155,14 +200,16 @@ def window_attention_prefill(q: torch.Tensor, cache_k: torch.Tensor, cache_v: to
         q = q if q.is_contiguous() else q.contiguous()
         out = torch.empty(B, T, H, Dv, dtype=q.dtype, device=q.device)
         qs, nn_, sid = _i32(q_start), _i32(n_new), _i32(seq_ids)
-        cargs, bt = _cache_args(cache_k, cache_v, block_table, page_size)
+        cargs, bt = _cache_args(cache_k, cache_v, block_table, page_size, rows=True)
+        sk = sinks.float().contiguous() if sinks is not None else None
         L = _lib.lib(GROUP)
-        rc = L.nxd_window_attn_prefill(_c.c_int(_code(q.dtype)), _lib.ptr(q), _lib.ptr(cache_k), _lib.ptr(cache_v),
+        rc = L.nxd_masked_attn_prefill(_c.c_int(_code(q.dtype)), _lib.ptr(q), _lib.ptr(cache_k), _lib.ptr(cache_v),
                                        *cargs, _lib.ptr(out), _lib.ptr(qs), _lib.ptr(nn_), _lib.ptr(sid),
-                                       _lib.ptr(slopes), _c.c_int(B), _c.c_int(T), _c.c_int(H), _c.c_int(G), _c.c_int(D),
-                                       _c.c_int(Dv), _c.c_float(scale), _c.c_int(w), _c.c_int(keep_first),
+                                       _lib.ptr(slopes), _lib.ptr(sk), _c.c_int(B), _c.c_int(T), _c.c_int(H), _c.c_int(G),
+                                       _c.c_int(D), _c.c_int(Dv), _c.c_float(scale), _c.c_int(w), _c.c_int(keep_first),
+                                       _c.c_int(int(chunk) if chunk else 0),
                                        _c.c_int({"auto": 0, "generic": 1, "mma": 2}[impl]), _lib.stream_ptr())
-        _lib.check(rc, "nxd_window_attn_prefill", L)
+        _lib.check(rc, "nxd_masked_attn_prefill", L)
         return out
     out = torch.zeros(B, T, H, Dv, dtype=q.dtype, device=q.device)
     for b in range(B):
@@ -174,7 +221,7 @@ def window_attention_prefill(q: torch.Tensor, cache_k: torch.Tensor, cache_v: to
         kk = _cache_rows(cache_k, line, p0 + n, block_table, page_size)
         vv = _cache_rows(cache_v, line, p0 + n, block_table, page_size)
         pos = torch.arange(p0, p0 + n, device=q.device)
-        out[b, :n] = window_attention_ref(q[b, :n], kk, vv, pos, scale, w, keep_first, slopes).to(q.dtype)
+        out[b, :n] = window_attention_ref(q[b, :n], kk, vv, pos, scale, w, keep_first, slopes, chunk, sinks).to(q.dtype)
     return out
 
 
@@ -182,7 +229,8 @@ def window_attention_decode(q: torch.Tensor, cache_k: torch.Tensor, cache_v: tor
                             scale: float, window: Optional[int] = None, keep_first: int = 0,
                             slopes: Optional[torch.Tensor] = None, seq_ids: Optional[torch.Tensor] = None,
                             block_table: Optional[torch.Tensor] = None, page_size: int = 0,
-                            impl: str = "auto") -> torch.Tensor:
+                            impl: str = "auto", chunk: Optional[int] = None,
+                            sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One new token per row: ``q [B, H, D]`` at ``positions[b]`` -> ``[B, H, Dv]``; only the kept first rows and the
     window's rows of the cache line are read."""
     B, H, D = q.shape
@@ -192,14 +240,15 @@ def window_attention_decode(q: torch.Tensor, cache_k: torch.Tensor, cache_v: tor
         q = q if q.is_contiguous() else q.contiguous()
         out = torch.empty(B, H, Dv, dtype=q.dtype, device=q.device)
         pos, sid = _i32(positions), _i32(seq_ids)
-        cargs, bt = _cache_args(cache_k, cache_v, block_table, page_size)
+        cargs, bt = _cache_args(cache_k, cache_v, block_table, page_size, rows=True)
+        sk = sinks.float().contiguous() if sinks is not None else None
         L = _lib.lib(GROUP)
-        rc = L.nxd_window_attn_decode(_c.c_int(_code(q.dtype)), _lib.ptr(q), _lib.ptr(cache_k), _lib.ptr(cache_v), *cargs,
-                                      _lib.ptr(out), _lib.ptr(pos), _lib.ptr(sid), _lib.ptr(slopes), _c.c_int(B),
-                                      _c.c_int(H), _c.c_int(G), _c.c_int(D), _c.c_int(Dv), _c.c_float(scale), _c.c_int(w),
-                                      _c.c_int(keep_first), _c.c_int({"auto": 0, "generic": 1, "mma": 2}[impl]),
-                                      _lib.stream_ptr())
-        _lib.check(rc, "nxd_window_attn_decode", L)
+        rc = L.nxd_masked_attn_decode(_c.c_int(_code(q.dtype)), _lib.ptr(q), _lib.ptr(cache_k), _lib.ptr(cache_v), *cargs,
+                                      _lib.ptr(out), _lib.ptr(pos), _lib.ptr(sid), _lib.ptr(slopes), _lib.ptr(sk),
+                                      _c.c_int(B), _c.c_int(H), _c.c_int(G), _c.c_int(D), _c.c_int(Dv), _c.c_float(scale),
+                                      _c.c_int(w), _c.c_int(keep_first), _c.c_int(int(chunk) if chunk else 0),
+                                      _c.c_int({"auto": 0, "generic": 1, "mma": 2}[impl]), _lib.stream_ptr())
+        _lib.check(rc, "nxd_masked_attn_decode", L)
         return out
     out = torch.empty(B, H, Dv, dtype=q.dtype, device=q.device)
     for b in range(B):
@@ -208,7 +257,7 @@ def window_attention_decode(q: torch.Tensor, cache_k: torch.Tensor, cache_v: tor
         kk = _cache_rows(cache_k, line, p + 1, block_table, page_size)
         vv = _cache_rows(cache_v, line, p + 1, block_table, page_size)
         out[b] = window_attention_ref(q[b:b + 1], kk, vv, torch.tensor([p], device=q.device), scale, w, keep_first,
-                                      slopes)[0].to(q.dtype)
+                                      slopes, chunk, sinks)[0].to(q.dtype)
     return out
 
 

@@ -58,3 +58,26 @@ class ZeroCenteredRMSNorm(torch.nn.Module):
 
     def add_to(self, stream: torch.Tensor, sublayer_out: torch.Tensor, out_dtype: torch.dtype = None):
         return norm_ops.post_norm_residual_(stream, sublayer_out, self.weight, self.variance_epsilon, out_dtype, offset=1.0)
+
+
+class WeightOnlyLayerNorm(torch.nn.Module):
+    """``(x - mean) / sqrt(var + eps) * w`` (no bias; variance of the deviations), weight and statistics in fp32, for
+    models that keep an fp32 residual stream with a norm BEFORE and AFTER every sublayer.  ``forward`` is the plain norm
+    of the stream; ``add_to(x, y, next_norm)`` does ``x += self(y)`` in place and, in the same pass, returns
+    ``next_norm(x)`` -- the next sublayer's input -- in ``out_dtype``."""
+
+    center = True
+
+    def __init__(self, hidden_size: int, eps: float = 1e-6, device=None):
+        super().__init__()
+        self.weight = torch.nn.Parameter(torch.ones(hidden_size, dtype=torch.float32, device=device))
+        self.variance_epsilon = eps
+
+    def forward(self, stream: torch.Tensor, out_dtype: torch.dtype = None) -> torch.Tensor:
+        return norm_ops.norm_chain_(stream, None, None, self.weight, self.variance_epsilon,
+                                    out_dtype or stream.dtype, center=self.center)[1]
+
+    def add_to(self, stream: torch.Tensor, sublayer_out: torch.Tensor, next_norm: "WeightOnlyLayerNorm" = None,
+               out_dtype: torch.dtype = None):
+        return norm_ops.norm_chain_(stream, sublayer_out, self.weight, next_norm.weight if next_norm is not None else None,
+                                    self.variance_epsilon, out_dtype, center=self.center)

@@ -55,10 +55,11 @@ def parse_args():
     ap.add_argument("--no-inference", action="store_true",
                     help="skip the second half of the headline metric (Llama-3.2-1B TTFT / decode tokens/s, reported "
                          "under the extra key \"inference\")")
-    ap.add_argument("--families", action="store_true",
-                    help="instead of the headline workload: serving throughput (prefill and decode tokens/s) of the "
-                         "Gekazen family next to the Mixtral-style decoder at equal layer sizes, and their like-for-like "
-                         "kernels with roofline fractions (1 GPU; one JSON line)")
+    ap.add_argument("--families", nargs="?", const="gekazen", default="", choices=["gekazen", "rasodra"],
+                    help="instead of the headline workload: serving throughput (prefill and decode tokens/s) of a "
+                         "family next to the closest existing decoder at equal layer sizes (gekazen: the Mixtral-style "
+                         "decoder; rasodra: the Llama decoder), and their like-for-like kernels with roofline fractions "
+                         "(1 GPU; one JSON line)")
     ap.add_argument("--profile", default="", help="diagnosis only: write a kernel timeline summary of 2 steps (rank 0) "
                     "to this file instead of timing (numbers under a profiler are never bench values)")
     return ap.parse_args()
@@ -435,7 +436,8 @@ def main():
         assert world == 1, "--families is a single-GPU comparison"
         sampler = ClockSampler(local_rank)
         sampler.start()
-        out = family_bench.run(steps=args.steps, warmup=args.warmup, device=dev)
+        bench_fn = family_bench.run_hybrid if args.families == "rasodra" else family_bench.run
+        out = bench_fn(steps=args.steps, warmup=args.warmup, device=dev)
         out["clocks"] = sampler.stop()
         print(json.dumps(out))
         return

@@ -208,3 +208,190 @@ def run(steps: int = 10, warmup: int = 3, device=None, sizes=None) -> dict:
         out["kernels"][s["name"]] = kernel_cases(s, steps, warmup, dev)
     out["gpu_launches"] = _lib.kernel_launches() - before
     return out
+
+
+# ---- Rasodra (chunked attention + recurrent matrix memory + latent attention, dense feed-forward) next to the Llama
+# decoder at equal width, heads, head size, layer count and feed-forward parameters -----------------------------------------
+HYBRID_SIZES = [
+    dict(name="w2048", width=2048, heads=16, kv_heads=4, dim=128, chunk=1024, rec_heads=4, rec_dim=128, rec_vdim=256,
+         lat_dim=128, lat_rot=64, lat_vdim=128, rank=512, ff=8192, prefill_batch=4, prompt=2048, decode_batch=16),
+    dict(name="w4096", width=4096, heads=32, kv_heads=8, dim=128, chunk=2048, rec_heads=8, rec_dim=256, rec_vdim=512,
+         lat_dim=128, lat_rot=64, lat_vdim=128, rank=512, ff=12288, prefill_batch=2, prompt=4096, decode_batch=32),
+    dict(name="w1024", width=1024, heads=16, kv_heads=4, dim=64, chunk=512, rec_heads=4, rec_dim=64, rec_vdim=128,
+         lat_dim=64, lat_rot=32, lat_vdim=64, rank=256, ff=4096, prefill_batch=8, prompt=1024, decode_batch=64),
+]
+
+
+def rasodra_config(s: dict):
+    from ..models.rasodra import RasodraConfig
+
+    ff = {"kind": "dense", "ff": s["ff"]}
+    att = {"type": "attention", "mlp": ff,
+           "mixer": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"],
+                     "scale": s["dim"] ** -0.5, "mask": {"size": s["chunk"]}, "rot": {"dims": s["dim"], "base": 500000.0}}}
+    rec = {"type": "mlstm", "mlp": None,
+           "mixer": {"heads": s["rec_heads"], "dim": s["rec_dim"], "vdim": s["rec_vdim"], "gate_cap": 15.0}}
+    lat = {"type": "latent_attention", "mlp": ff,
+           "mixer": {"heads": s["heads"], "dim": s["lat_dim"], "rot_dim": s["lat_rot"], "vdim": s["lat_vdim"],
+                     "kv_rank": s["rank"], "scale": (s["lat_dim"] + s["lat_rot"]) ** -0.5,
+                     "rot": {"dims": s["lat_rot"], "base": 1000000.0}}}
+    return RasodraConfig.from_dict({"architecture": "Rasodra", "vocab": VOCAB, "width": s["width"], "norm": {"eps": 1e-6},
+                                    "layers": [att, rec, lat, lat]}, torch_dtype=torch.bfloat16)
+
+
+def llama_like_config(s: dict):
+    from ..models.llama import LlamaConfig
+
+    # three matrices of (width x i) against two of (width x ff): i = 2/3 ff keeps the feed-forward parameters equal
+    inter = (2 * s["ff"] // 3 + 127) // 128 * 128
+    return LlamaConfig(vocab_size=VOCAB, hidden_size=s["width"], intermediate_size=inter, num_hidden_layers=4,
+                       num_attention_heads=s["heads"], num_key_value_heads=s["kv_heads"], head_dim=s["dim"],
+                       rope_scaling=None, max_position_embeddings=s["prompt"] + 64, tie_word_embeddings=False,
+                       sequence_parallel_enabled=False, torch_dtype=torch.bfloat16)
+
+
+def hybrid_serve_case(s: dict, steps: int, warmup: int, dev) -> dict:
+    from .hybrid import RasodraInferenceModel
+    from .model import LlamaInferenceModel
+
+    timer = _Timer(dev)
+    out = {"size": dict(s)}
+    ic = dict(batch_size=s["decode_batch"], max_batch_size=s["decode_batch"], max_context_length=s["prompt"],
+              seq_len=s["prompt"] + 64, is_continuous_batching=True, use_cuda_graphs=False)
+    for name, make in (("rasodra", lambda: RasodraInferenceModel(rasodra_config(s), InferenceConfig(**ic), device=dev)),
+                       ("llama", lambda: LlamaInferenceModel(llama_like_config(s), InferenceConfig(**ic), device=dev))):
+        torch.manual_seed(0)
+        model = make()
+        model.init_kv_cache(device=dev)
+        out[name] = _serve(model, s, timer, steps, warmup, dev)
+        del model
+        torch.cuda.empty_cache()
+    out["rasodra_over_llama"] = {k: out["rasodra"][k] / out["llama"][k]
+                                 for k in ("prefill_tokens_per_s", "decode_tokens_per_s")}
+    return out
+
+
+def hybrid_kernel_cases(s: dict, steps: int, warmup: int, dev) -> List[dict]:
+    """The mixers' own kernels on the shapes of ``s``, alone, with roofline fractions, next to the like kernel of the
+    Llama decoder (flash attention forward, decode attention over the full context, fused add + RMSNorm)."""
+    from ..ops import latent_attention as la
+    from ..ops import mlstm as ml
+    from ..ops import rope as rope_ops
+
+    pk = peaks()
+    timer = _Timer(dev)
+    bf = torch.bfloat16
+    B, T, H, G, D, W, Bd = s["prefill_batch"], s["prompt"], s["heads"], s["kv_heads"], s["dim"], s["width"], s["decode_batch"]
+    rows = []
+
+    def row(kernel, like, ms, flops=None, nbytes=None):
+        r = {"kernel": kernel, "like": like, "ms": ms, "peak": pk["source"]}
+        if flops is not None:
+            r["tflops"] = flops / ms / 1e9
+            r["of_peak"] = r["tflops"] / pk["bf16_tflops"]
+        if nbytes is not None:
+            r["gbs"] = nbytes / ms / 1e6
+            r["of_peak"] = r["gbs"] / pk["hbm_gbs"]
+        rows.append(r)
+
+    S = T + 64
+    zero = torch.zeros(B, dtype=torch.int32, device=dev)
+    i = torch.arange(T).reshape(T, 1)
+    j = torch.arange(T).reshape(1, T)
+    pairs_chunk = int(((j <= i) & (i // s["chunk"] == j // s["chunk"])).sum())
+    pairs_causal = T * (T + 1) // 2
+    # chunked attention, prefill and decode
+    q = torch.randn(B, T, H, D, device=dev, dtype=bf)
+    ck = torch.randn(max(B, Bd), G, S, D, device=dev, dtype=bf)
+    cv = torch.randn(max(B, Bd), G, S, D, device=dev, dtype=bf)
+    ms = timer(lambda: wa.window_attention_prefill(q, ck, cv, zero, D ** -0.5, chunk=s["chunk"]), steps, warmup)
+    row("chunked attention prefill (mma.sync, over the cache)", "prefill attention", ms, flops=4.0 * D * pairs_chunk * H * B)
+    qh, kh, vh = q.permute(0, 2, 1, 3), ck[:B, :, :T], cv[:B, :, :T]
+    ms = timer(lambda: attn_ops.flash_attn_func(qh, kh, vh, causal=True), steps, warmup)
+    row("flash attention forward (tcgen05, plain causal)", "prefill attention", ms, flops=4.0 * D * pairs_causal * H * B)
+    qd = torch.randn(Bd, H, D, device=dev, dtype=bf)
+    posd = torch.full((Bd,), T, dtype=torch.int32, device=dev)
+    seen = T % s["chunk"] + 1
+    ms = timer(lambda: wa.window_attention_decode(qd, ck, cv, posd, D ** -0.5, chunk=s["chunk"]), steps, warmup)
+    row("chunked attention decode (rows of the query's chunk)", "decode attention", ms, nbytes=2.0 * seen * G * 2 * D * Bd)
+    posm = torch.full((Bd,), T - 1, dtype=torch.int32, device=dev)
+    ms = timer(lambda: wa.window_attention_decode(qd, ck, cv, posm, D ** -0.5, chunk=s["chunk"]), steps, warmup)
+    row("chunked attention decode (a full chunk)", "decode attention", ms,
+        nbytes=2.0 * ((T - 1) % s["chunk"] + 1) * G * 2 * D * Bd)
+    lens = torch.full((Bd,), T + 1, dtype=torch.int32, device=dev)
+    ms = timer(lambda: attn_ops.decode_attention(qd, ck, cv, lens), steps, warmup)
+    row("decode attention (full context)", "decode attention", ms, nbytes=2.0 * (T + 1) * G * 2 * D * Bd)
+    del ck, cv
+    # latent attention: prefill over expanded heads, decode over the latent rows
+    Dn, Dr, Dv, R = s["lat_dim"], s["lat_rot"], s["lat_vdim"], s["rank"]
+    ql = torch.randn(B, T, H, Dn + Dr, device=dev, dtype=bf)
+    kx = torch.randn(B, T, H, Dn + Dr, device=dev, dtype=bf).permute(0, 2, 1, 3)
+    vx = torch.randn(B, T, H, Dv, device=dev, dtype=bf).permute(0, 2, 1, 3)
+    sinks = torch.zeros(H, device=dev)
+    ms = timer(lambda: wa.window_attention_prefill(ql, kx, vx, zero, 0.07, sinks=sinks), steps, warmup)
+    row("latent attention prefill (expanded heads, sink)", "prefill attention", ms,
+        flops=2.0 * (Dn + Dr + Dv) * pairs_causal * H * B)
+    cl = torch.randn(Bd, 1, S, R + Dr, device=dev, dtype=bf)
+    qa = torch.randn(Bd, H, R + Dr, device=dev, dtype=bf)
+    ms = timer(lambda: wa.window_attention_decode(qa, cl, cl[..., :R], posd, 0.07, sinks=sinks), steps, warmup)
+    row("latent attention decode (absorbed queries over latent rows)", "decode attention", ms,
+        nbytes=2.0 * (T + 1) * (R + Dr) * Bd)
+    proj = torch.randn(B, T, H * (Dn + Dr) + R + Dr, device=dev, dtype=bf)
+    tables = rope_ops.build_interleaved_rope_cache(S, Dr, 1e6, device=dev)
+    wn = torch.ones(R, device=dev)
+    ms = timer(lambda: la.latent_prep(proj, 0, H * (Dn + Dr), None, cl, wn, tables, zero, H, Dn, Dr, R, 1e-6), steps, warmup)
+    row("latent norm + rotations + cache row", "projection epilogue", ms,
+        nbytes=2.0 * B * T * (2 * H * (Dn + Dr) + 2 * (R + Dr)))
+    del cl
+    # recurrent matrix memory
+    Hr, Dk, Dvr = s["rec_heads"], s["rec_dim"], s["rec_vdim"]
+    ld = 2 * Hr * Dk + 2 * Hr * Dvr
+    pr = torch.randn(B, T, ld, device=dev, dtype=bf) * 0.3
+    gi = torch.randn(B * T, Hr, device=dev)
+    gf = -torch.rand(B * T, Hr, device=dev) * 0.1
+    st = (torch.zeros(Bd, Hr, Dk, Dvr, device=dev), torch.zeros(Bd, Hr, Dk, device=dev), torch.zeros(Bd, Hr, device=dev))
+    ms = timer(lambda: ml.mlstm_scan(pr, (0, Hr * Dk, 2 * Hr * Dk), gi, gf, st, zero, Hr, Dk, Dvr, Dk ** -0.5), steps, warmup)
+    row("recurrent scan, prompt (token by token in registers)", "prefill attention", ms,
+        flops=6.0 * Dk * Dvr * Hr * B * T)
+    prd = torch.randn(Bd, 1, ld, device=dev, dtype=bf) * 0.3
+    one = torch.ones(Bd, dtype=torch.int32, device=dev)
+    ms = timer(lambda: ml.mlstm_scan(prd, (0, Hr * Dk, 2 * Hr * Dk), gi[:Bd], gf[:Bd], st, one, Hr, Dk, Dvr, Dk ** -0.5),
+               steps, warmup)
+    row("recurrent scan, one token (state read + written)", "decode attention", ms, nbytes=8.0 * Dk * Dvr * Hr * Bd)
+    hh = torch.randn(B * T, W, device=dev, dtype=bf)
+    gw = torch.randn(2 * Hr, W, device=dev, dtype=bf) * 0.02
+    gb = torch.zeros(2 * Hr, device=dev)
+    ms = timer(lambda: ml.mlstm_gates(hh, gw, gb, Hr, 15.0), steps, warmup)
+    row("recurrent gates (fp32 dot products)", "norm", ms, nbytes=2.0 * B * T * W)
+    # norms on the prefill activations
+    N = B * T
+    x32 = torch.randn(N, W, device=dev)
+    y = torch.randn(N, W, device=dev, dtype=bf)
+    w1, w2 = torch.ones(W, device=dev), torch.ones(W, device=dev)
+    ms = timer(lambda: norm_ops.norm_chain_(x32, y, w1, w2, 1e-6, bf), steps, warmup)
+    row("post-norm + fp32 residual + next pre-norm", "norm", ms, nbytes=float(N * W * (2 + 4 + 4 + 2)))
+    rb, wb = torch.randn(N, W, device=dev, dtype=bf), torch.ones(W, device=dev, dtype=bf)
+    ms = timer(lambda: norm_ops.fused_add_rms_norm(y, rb, wb, 1e-5), steps, warmup)
+    row("fused add + RMSNorm (bf16 residual)", "norm", ms, nbytes=float(N * W * 2 * 4))
+    qk = torch.randn(B, T, (H + G) * D, device=dev, dtype=bf)
+    ck2 = torch.zeros(B, G, S, D, device=dev, dtype=bf)
+    cv2 = torch.zeros(B, G, S, D, device=dev, dtype=bf)
+    t2 = rope_ops.build_interleaved_rope_cache(S, D, 5e5, device=dev)
+    wq = torch.ones(D, device=dev)
+    ms = timer(lambda: wa.qk_norm_cache_write(qk, ck2, cv2, zero, H, G, D, D, 1e-6, q_weight=wq, k_weight=wq, rope=t2,
+                                              value_from_key=True), steps, warmup)
+    row("q/k norm + rotation + cache write", "projection epilogue", ms, nbytes=2.0 * N * (2 * H * D + 3 * G * D))
+    return rows
+
+
+def run_hybrid(steps: int = 10, warmup: int = 3, device=None, sizes=None) -> dict:
+    dev = device or torch.device("cuda", torch.cuda.current_device())
+    before = _lib.kernel_launches()
+    out = {"metric": "Rasodra vs Llama decoder, serving throughput at equal layer sizes", "dtype": "bf16",
+           "data": "synthetic token ids, random-init weights", "steps": steps, "warmup": max(warmup, 3),
+           "l2": "192 MB written between timed runs", "peaks": peaks(), "cases": [], "kernels": {}}
+    for s in (sizes or HYBRID_SIZES):
+        out["cases"].append(hybrid_serve_case(s, steps, warmup, dev))
+        out["kernels"][s["name"]] = hybrid_kernel_cases(s, steps, warmup, dev)
+    out["gpu_launches"] = _lib.kernel_launches() - before
+    return out

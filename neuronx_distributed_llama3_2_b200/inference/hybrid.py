@@ -111,6 +111,24 @@ class RasodraInferenceModel(KVCacheInferenceMixin, RasodraForCausalLM):
                                                 **paged)
         return mixer.o_proj(o.reshape(B, T, m.heads * m.vdim))
 
+    def _latent_rows(self, ck, lines, n_ctx: int) -> torch.Tensor:
+        """Rows ``[0, n_ctx)`` of the given cache lines of a latent cache tensor, ``[len(lines), n_ctx, rank + rot]``."""
+        kc = self.kv_cache
+        if not kc.paged:
+            return ck[lines.long(), 0, :n_ctx]
+        n_pages = (n_ctx + kc.page_size - 1) // kc.page_size
+        pages = kc.block_table[lines.long(), :n_pages].long()                      # [B, n_pages]
+        return ck[pages][:, :, 0].reshape(pages.shape[0], n_pages * kc.page_size, ck.shape[-1])[:, :n_ctx]
+
+    def _step_context_len(self, q_start, n_new, T: int) -> int:
+        """Positions that the step's rows reach at most.  A step that starts every row at position 0 needs no look at the
+        device (T, which keeps the step capturable in a CUDA graph); a step of portions reads it back once."""
+        if not self._step_past_context:
+            return T
+        if "n_ctx" not in self._step_kv:
+            self._step_kv["n_ctx"] = int((q_start + (n_new if n_new is not None else T)).max())
+        return self._step_kv["n_ctx"]
+
     def _mix_latent(self, i, mixer, h, q_start, n_new, seq_ids):
         m, cfg, dt = mixer.cfg, self.config, self.config.torch_dtype
         B, T, _ = h.shape
@@ -118,19 +136,34 @@ class RasodraInferenceModel(KVCacheInferenceMixin, RasodraForCausalLM):
         ck, cv = self.kv_cache.layer(i)                    # cv: the first kv_rank columns of ck's rows
         paged = self._paged()
         proj = mixer.in_proj(h)
-        q_abs = torch.empty(N, H, R + m.rot_dim, dtype=dt, device=h.device)
-        q_nope = la_ops.latent_prep(proj, 0, mixer.q_cols, q_abs, ck, mixer.kv_norm, self._rotary_tables(m.rot, h.device),
-                                    q_start, H, m.dim, m.rot_dim, R, cfg.rms_norm_eps, n_new=n_new, seq_ids=seq_ids,
-                                    **paged)
-        # absorption: W_uk_h^T q_nope_h for every head in one batched product
-        q_abs[..., :R] = torch.bmm(q_nope.transpose(0, 1), mixer.uk).transpose(0, 1)
+        rope = self._rotary_tables(m.rot, h.device)
         if T == 1:
+            # token generation: absorbed queries over the latent rows, value projection after the attention
+            q_abs = torch.empty(N, H, R + m.rot_dim, dtype=dt, device=h.device)
+            q_nope = la_ops.latent_prep(proj, 0, mixer.q_cols, q_abs, ck, mixer.kv_norm, rope, q_start, H, m.dim,
+                                        m.rot_dim, R, cfg.rms_norm_eps, n_new=n_new, seq_ids=seq_ids, **paged)
+            q_abs[..., :R] = torch.bmm(q_nope.transpose(0, 1), mixer.uk).transpose(0, 1)
             o_lat = wa_ops.window_attention_decode(q_abs, ck, cv, q_start, m.scale, seq_ids=seq_ids, sinks=mixer.sink,
                                                    **paged)
+            o = torch.bmm(o_lat.transpose(0, 1), mixer.uv.transpose(1, 2)).transpose(0, 1).contiguous()   # [N, H, vdim]
         else:
-            o_lat = wa_ops.window_attention_prefill(q_abs.reshape(B, T, H, R + m.rot_dim), ck, cv, q_start, m.scale,
-                                                    n_new=n_new, seq_ids=seq_ids, sinks=mixer.sink, **paged)
-        o = torch.bmm(o_lat.reshape(N, H, R).transpose(0, 1), mixer.uv_t).transpose(0, 1).contiguous()   # [N, H, vdim]
+            # prompt steps: per-head keys and values expanded from the latent rows of every line of the step (all
+            # positions up to the step's end: a portion at an offset sees the earlier rows too), then attention with
+            # head size dim + rot; the expansion is two matrix products over the rows
+            q = la_ops.latent_prep(proj, 0, mixer.q_cols, None, ck, mixer.kv_norm, rope, q_start, H, m.dim, m.rot_dim, R,
+                                   cfg.rms_norm_eps, n_new=n_new, seq_ids=seq_ids, **paged)
+            n_ctx = self._step_context_len(q_start, n_new, T)
+            from ..ops.linear import gemm_nt
+            lines = seq_ids if seq_ids is not None else torch.arange(B, device=h.device)
+            rows = self._latent_rows(ck, lines, n_ctx)                               # [B, n_ctx, R + rot]
+            c = rows[..., :R].reshape(B * n_ctx, R)
+            keys = torch.empty(B, n_ctx, H, m.dim + m.rot_dim, dtype=dt, device=h.device)
+            keys[..., :m.dim] = gemm_nt(c.contiguous(), mixer.uk.reshape(H * m.dim, R)).reshape(B, n_ctx, H, m.dim)
+            keys[..., m.dim:] = rows[..., R:].unsqueeze(2)
+            vals = gemm_nt(c.contiguous(), mixer.uv.reshape(H * m.vdim, R)).reshape(B, n_ctx, H, m.vdim)
+            o = wa_ops.window_attention_prefill(q.reshape(B, T, H, m.dim + m.rot_dim), keys.permute(0, 2, 1, 3),
+                                                vals.permute(0, 2, 1, 3), q_start, m.scale, n_new=n_new,
+                                                sinks=mixer.sink).reshape(N, H, m.vdim)
         y = mlstm_ops.head_norm_gate(o, proj.reshape(N, -1), mixer.q_cols + mixer.kv_cols, H, m.vdim, None,
                                      cfg.rms_norm_eps, False, dt)
         return mixer.o_proj(y.reshape(B, T, H * m.vdim))

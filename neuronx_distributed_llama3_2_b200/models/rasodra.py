@@ -230,8 +230,10 @@ class ChunkedAttentionMixer(nn.Module):
 
 class LatentAttentionMixer(nn.Module):
     """q | compressed kv (+ shared rotated key part) | output gate in one projection; latent norm weight; per-head
-    up-projections kept as ``uk [heads, dim, rank]`` (absorbed into the query) and ``uv_t [heads, rank, vdim]`` (applied
-    to the attention output); sink logits; output projection."""
+    up-projections kept per head, ``uk [heads, dim, rank]`` and ``uv [heads, vdim, rank]``: token generation absorbs
+    ``uk`` into the query and applies ``uv`` to the attention output over the latent rows; prompt steps expand keys and
+    values from the latent rows with the same two tensors viewed as ``[heads * dim, rank]`` / ``[heads * vdim, rank]``;
+    sink logits; output projection."""
 
     def __init__(self, config: RasodraConfig, m: LatentAttentionConfig, device=None):
         super().__init__()
@@ -242,7 +244,7 @@ class LatentAttentionMixer(nn.Module):
         self.in_proj = _linear_in(config, self.q_cols + self.kv_cols + m.heads * m.vdim, False, device)
         self.kv_norm = nn.Parameter(torch.ones(m.kv_rank, dtype=torch.float32, device=device))
         self.uk = nn.Parameter(torch.empty(m.heads, m.dim, m.kv_rank, dtype=dt, device=device).normal_(0.0, std))
-        self.uv_t = nn.Parameter(torch.empty(m.heads, m.kv_rank, m.vdim, dtype=dt, device=device).normal_(0.0, std))
+        self.uv = nn.Parameter(torch.empty(m.heads, m.vdim, m.kv_rank, dtype=dt, device=device).normal_(0.0, std))
         self.sink = nn.Parameter(torch.zeros(m.heads, dtype=torch.float32, device=device))
         self.o_proj = _linear_out(config, m.heads * m.vdim, device)
 
@@ -330,7 +332,7 @@ def convert_rasodra_state_dict(sd: Dict[str, torch.Tensor], config: RasodraConfi
             out[dst + "mixer.in_proj.weight"] = torch.cat([mix("q"), mix("dkv"), mix("g")], dim=0)
             out[dst + "mixer.kv_norm"] = mix("dkv.norm").float()
             out[dst + "mixer.uk"] = mix("uk").reshape(m.heads, m.dim, m.kv_rank)
-            out[dst + "mixer.uv_t"] = mix("uv").reshape(m.heads, m.vdim, m.kv_rank).transpose(1, 2)
+            out[dst + "mixer.uv"] = mix("uv").reshape(m.heads, m.vdim, m.kv_rank)
             out[dst + "mixer.sink"] = mix("sink").float()
         elif L.type == "mlstm":
             out[dst + "mixer.in_proj.weight"] = torch.cat([mix("q"), mix("k"), mix("v"), mix("g")], dim=0)
@@ -366,7 +368,7 @@ def export_rasodra_state_dict(model: RasodraForCausalLM) -> Dict[str, torch.Tens
             out[dst + "mix.q"], out[dst + "mix.dkv"], out[dst + "mix.g"] = w[:nq], w[nq:nq + nkv], w[nq + nkv:]
             out[dst + "mix.dkv.norm"] = sd[src + "mixer.kv_norm"]
             out[dst + "mix.uk"] = sd[src + "mixer.uk"].reshape(m.heads * m.dim, m.kv_rank)
-            out[dst + "mix.uv"] = sd[src + "mixer.uv_t"].transpose(1, 2).reshape(m.heads * m.vdim, m.kv_rank)
+            out[dst + "mix.uv"] = sd[src + "mixer.uv"].reshape(m.heads * m.vdim, m.kv_rank)
             out[dst + "mix.sink"] = sd[src + "mixer.sink"]
         elif L.type == "mlstm":
             w, g, gb = sd[src + "mixer.in_proj.weight"], sd[src + "mixer.gate_weight"], sd[src + "mixer.gate_bias"]

@@ -29,39 +29,46 @@ def _i32(t):
     return t if (t.dtype == torch.int32 and t.is_contiguous()) else t.to(torch.int32).contiguous()
 
 
-def latent_prep(proj: torch.Tensor, q_off: int, kv_off: int, q_abs: torch.Tensor, cache: torch.Tensor,
+def latent_prep(proj: torch.Tensor, q_off: int, kv_off: int, q_abs: Optional[torch.Tensor], cache: torch.Tensor,
                 c_weight: torch.Tensor, rope: Tuple[torch.Tensor, torch.Tensor], q_start: torch.Tensor, heads: int,
                 dim: int, rot: int, rank: int, eps: float, n_new: Optional[torch.Tensor] = None,
                 seq_ids: Optional[torch.Tensor] = None, block_table: Optional[torch.Tensor] = None,
                 page_size: int = 0) -> torch.Tensor:
-    """``proj [B, T, ld]``.  Returns ``q_nope [B*T, heads, dim]`` (the un-rotated query columns, for the absorption
-    product) and fills ``q_abs[..., rank:]`` (``q_abs [B*T, heads, rank + rot]``) with the rotated query part; writes the
-    cache row ``[c | k_rot]`` of every real token at (line, position).  ``cache [lines | pages, 1, rows, rank + rot]``."""
+    """``proj [B, T, ld]``.  Writes the cache row ``[c | k_rot]`` of every real token at (line, position);
+    ``cache [lines | pages, 1, rows, rank + rot]``.  With ``q_abs [B*T, heads, rank + rot]`` (token generation): returns
+    ``q_nope [B*T, heads, dim]`` (the un-rotated query columns, for the absorption product) and fills
+    ``q_abs[..., rank:]`` with the rotated query part.  With ``q_abs=None`` (prompt steps): returns the queries
+    ``[B*T, heads, dim + rot]`` with their rotated part turned."""
     B, T, ld = proj.shape
     N = B * T
     cos, sin = rope
-    q_nope = torch.empty(N, heads, dim, dtype=proj.dtype, device=proj.device)
+    if q_abs is None:
+        q_full = torch.empty(N, heads, dim + rot, dtype=proj.dtype, device=proj.device)
+        q_nope, nope_head, q_rot, rot_head, ret = q_full, dim + rot, q_full[..., dim:], dim + rot, q_full
+    else:
+        q_nope = torch.empty(N, heads, dim, dtype=proj.dtype, device=proj.device)
+        nope_head, q_rot, rot_head, ret = dim, q_abs[..., rank:], rank + rot, q_nope
     if proj.is_cuda and proj.dtype in (torch.bfloat16, torch.float32) and _lib.available(GROUP):
-        assert proj.is_contiguous() and q_abs.is_contiguous() and cache.stride(3) == 1
-        bt = _i32(block_table)
+        assert proj.is_contiguous() and (q_abs is None or q_abs.is_contiguous()) and cache.stride(3) == 1
+        bt, qs, nn_, sid = _i32(block_table), _i32(q_start), _i32(n_new), _i32(seq_ids)   # alive across the launch
         max_pos = bt.shape[1] * page_size if bt is not None else cache.shape[2]
         L = _lib.lib(GROUP)
-        es = proj.element_size()
         rc = L.nxd_latent_prep(_c.c_int({torch.bfloat16: 0, torch.float32: 1}[proj.dtype]), _lib.ptr(proj),
-                               _c.c_longlong(ld), _c.c_int(q_off), _c.c_int(kv_off), _lib.ptr(q_nope), _c.c_longlong(dim),
-                               _c.c_void_p(q_abs.data_ptr() + rank * es), _c.c_longlong(rank + rot), _lib.ptr(cache),
+                               _c.c_longlong(ld), _c.c_int(q_off), _c.c_int(kv_off), _lib.ptr(q_nope),
+                               _c.c_longlong(nope_head), _c.c_void_p(q_rot.data_ptr()), _c.c_longlong(rot_head),
+                               _lib.ptr(cache),
                                _c.c_longlong(cache.stride(0)), _c.c_longlong(cache.stride(2)), _lib.ptr(bt),
                                _c.c_int(page_size if bt is not None else 0), _c.c_int(bt.shape[1] if bt is not None else 0),
-                               _lib.ptr(c_weight), _lib.ptr(cos), _lib.ptr(sin), _lib.ptr(_i32(q_start)),
-                               _lib.ptr(_i32(n_new)), _lib.ptr(_i32(seq_ids)), _c.c_int(B), _c.c_int(T), _c.c_int(heads),
+                               _lib.ptr(c_weight), _lib.ptr(cos), _lib.ptr(sin), _lib.ptr(qs),
+                               _lib.ptr(nn_), _lib.ptr(sid), _c.c_int(B), _c.c_int(T), _c.c_int(heads),
                                _c.c_int(dim), _c.c_int(rot), _c.c_int(rank), _c.c_float(eps), _c.c_int(max_pos),
                                _lib.stream_ptr())
         _lib.check(rc, "nxd_latent_prep", L)
-        return q_nope
+        return ret
     pos = q_start.long().reshape(B, 1) + torch.arange(T, device=proj.device).reshape(1, T)
     q = proj[..., q_off: q_off + heads * (dim + rot)].reshape(B, T, heads, dim + rot)
-    q_nope.copy_(q[..., :dim].reshape(N, heads, dim))
-    q_abs[..., rank:] = rope_interleaved_ref(q[..., dim:].float(), pos, cos, sin).to(proj.dtype).reshape(N, heads, rot)
+    q_nope[..., :dim] = q[..., :dim].reshape(N, heads, dim)
+    q_rot.copy_(rope_interleaved_ref(q[..., dim:].float(), pos, cos, sin).to(proj.dtype).reshape(N, heads, rot))
     kv = proj[..., kv_off: kv_off + rank + rot].float()
     c = kv[..., :rank]
     c = c / torch.sqrt(c.pow(2).mean(-1, keepdim=True) + eps) * c_weight.float()
@@ -76,4 +83,4 @@ def latent_prep(proj: torch.Tensor, q_off: int, kv_off: int, q_abs: torch.Tensor
                 cache[int(block_table[line, p // page_size]), 0, p % page_size] = rows[b, t]
             else:
                 cache[line, 0, p] = rows[b, t]
-    return q_nope
+    return ret

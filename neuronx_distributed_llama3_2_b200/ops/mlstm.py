@@ -78,11 +78,12 @@ def mlstm_scan(proj: torch.Tensor, offsets: Tuple[int, int, int], gi: torch.Tens
         out = torch.empty(B, T, heads, vdim, dtype=torch.float32, device=proj.device)
         nxn = torch.empty(B, heads, dim, dtype=torch.float32, device=proj.device)
         nxm = torch.empty(B, heads, dtype=torch.float32, device=proj.device)
+        qs, nn_, sid = _i32(q_start), _i32(n_new), _i32(seq_ids)      # converted copies stay alive across the launch
         L = _lib.lib(GROUP)
         rc = L.nxd_mlstm_scan(_c.c_int(_code(proj.dtype)), _lib.ptr(proj), _c.c_longlong(ld), _c.c_int(offsets[0]),
                               _c.c_int(offsets[1]), _c.c_int(offsets[2]), _lib.ptr(gi), _lib.ptr(gf), _lib.ptr(S),
-                              _lib.ptr(n), _lib.ptr(m), _lib.ptr(nxn), _lib.ptr(nxm), _lib.ptr(out), _lib.ptr(_i32(q_start)),
-                              _lib.ptr(_i32(n_new)), _lib.ptr(_i32(seq_ids)), _c.c_int(B), _c.c_int(T), _c.c_int(heads),
+                              _lib.ptr(n), _lib.ptr(m), _lib.ptr(nxn), _lib.ptr(nxm), _lib.ptr(out), _lib.ptr(qs),
+                              _lib.ptr(nn_), _lib.ptr(sid), _c.c_int(B), _c.c_int(T), _c.c_int(heads),
                               _c.c_int(dim), _c.c_int(vdim), _c.c_float(qscale), _lib.stream_ptr())
         _lib.check(rc, "nxd_mlstm_scan", L)
         return out

@@ -234,8 +234,8 @@ def test_latent_rows_and_absorbed_queries_equal_expanded_keys_and_values(dev, dt
     q_abs[..., :C] = torch.bmm(q_nope.transpose(0, 1), uk).transpose(0, 1)
     o_lat = wa.window_attention_prefill(q_abs[None], cache, cache[..., :C], torch.tensor([0], device=dev), m["scale"],
                                         seq_ids=line, sinks=sd["l0.mix.sink"].to(dev))
-    uv_t = sd["l0.mix.uv"].reshape(H, Dv, C).transpose(1, 2).to(dev, dt)
-    o = torch.bmm(o_lat[0].transpose(0, 1), uv_t).transpose(0, 1).contiguous()
+    uv = sd["l0.mix.uv"].reshape(H, Dv, C).to(dev, dt)
+    o = torch.bmm(o_lat[0].transpose(0, 1), uv.transpose(1, 2)).transpose(0, 1).contiguous()
     y = ml.head_norm_gate(o, proj[0], H * (D + R) + C + R, H, Dv, None, 1e-6, False, dt)
     close(y.to("cpu", F64) @ W["l0.mix.o"].T, ref, dt, scale=3.0)
 

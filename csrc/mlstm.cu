@@ -188,6 +188,35 @@ __global__ void mlstm_commit_kernel(const float* __restrict__ next_n, const floa
     if (threadIdx.x == 0) state_m[(long long)line * H + hd] = next_m[(long long)b * H + hd];
 }
 
+// Chunk-wise form of the same recurrence, the part that is sequential over chunks.  For chunk c of a (row, head) pair,
+// u[c] holds the chunk's own contribution sum_s w_s k_s v_s^T (or sum_s w_s k_s), weighted relative to the chunk's local
+// maximum mloc[c], and ftot[c] the sum of the chunk's log forget gates.  Walking the chunks in order,
+//   m' = max(ftot[c] + m, mloc[c]);   s' = exp(ftot[c] + m - m') s + exp(mloc[c] - m') u[c]
+// and u[c] is REPLACED by the state at the chunk's start (what the chunk's outputs need).  One thread per state element.
+__global__ void mlstm_chunk_states_kernel(float* __restrict__ u, const float* __restrict__ ftot,
+                                          const float* __restrict__ mloc, const float* __restrict__ s0,
+                                          const float* __restrict__ m0, float* __restrict__ s_out,
+                                          float* __restrict__ m_start, float* __restrict__ m_out, int NC, long long E) {
+    const long long bh = blockIdx.y;
+    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= E) return;
+    float s = s0[bh * E + e];
+    float m = m0[bh];
+    for (int c = 0; c < NC; ++c) {
+        const float ft = ftot[bh * NC + c], ml = mloc[bh * NC + c];
+        const float mn = fmaxf(ft + m, ml);
+        const float a = expf(ft + m - mn), b = expf(ml - mn);
+        float* up = u + (bh * NC + c) * E + e;
+        const float uv = *up;
+        *up = s;
+        if (e == 0 && m_start != nullptr) m_start[bh * NC + c] = m;
+        s = fmaf(a, s, b * uv);
+        m = mn;
+    }
+    s_out[bh * E + e] = s;
+    if (e == 0 && m_out != nullptr) m_out[bh] = m;
+}
+
 template <typename T, int DPT>
 int launch_scan(const void* proj, long long ld, int q_off, int k_off, int v_off, const float* gi, const float* gf,
                 float* ss, float* sn, float* sm, float* nxn, float* nxm, float* out, const int* q_start, const int* n_new,
@@ -331,6 +360,19 @@ NXD_API int nxd_relu_squared(int dtype, const void* x, void* y, long long n, voi
         relu_squared_kernel<bf16><<<blocks, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)y, n);
     else
         relu_squared_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((const float*)x, (float*)y, n);
+    NXD_LAUNCH_CHECK();
+    return 0;
+}
+
+// u [BH, NC, E] fp32 (in: per-chunk contributions, out: state at every chunk's start); ftot, mloc [BH, NC]; s0 [BH, E],
+// m0 [BH]: state before the first chunk; s_out [BH, E]: state after the last; m_start [BH, NC] and m_out [BH] may be NULL.
+NXD_API int nxd_mlstm_chunk_states(float* u, const float* ftot, const float* mloc, const float* s0, const float* m0,
+                                   float* s_out, float* m_start, float* m_out, long long BH, int NC, long long E,
+                                   void* stream) {
+    if (BH == 0 || E == 0) return 0;
+    NXD_REQUIRE(BH < 65536, "recurrent mixer: %lld (row, head) pairs in one launch", BH);
+    dim3 grid((unsigned)((E + 255) / 256), (unsigned)BH);
+    mlstm_chunk_states_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(u, ftot, mloc, s0, m0, s_out, m_start, m_out, NC, E);
     NXD_LAUNCH_CHECK();
     return 0;
 }

@@ -27,6 +27,7 @@ import torch
 
 from ..models.rasodra import RasodraConfig, RasodraForCausalLM
 from ..ops import activation as act_ops
+from ..ops import attention as attn_ops
 from ..ops import latent_attention as la_ops
 from ..ops import mlstm as mlstm_ops
 from ..ops import rope as rope_ops
@@ -94,6 +95,13 @@ class RasodraInferenceModel(KVCacheInferenceMixin, RasodraForCausalLM):
         kc = self.kv_cache
         return dict(block_table=kc.block_table, page_size=kc.page_size) if kc.paged else {}
 
+    TC_PREFILL_MIN_TOKENS = 128          # shorter steps stay on the cache-reading kernels
+
+    def _chunks_as_batch(self, qk, m, T: int) -> bool:
+        return (T >= self.TC_PREFILL_MIN_TOKENS and not self._step_past_context and not self.kv_cache.paged
+                and (not m.chunk or T <= m.chunk or T % m.chunk == 0)
+                and wa_ops.tc_prefill_applies(qk, m.dim, m.vdim, qk.shape[-1]))
+
     def _mix_attention(self, i, mixer, h, q_start, n_new, seq_ids):
         m, cfg = mixer.cfg, self.config
         B, T, _ = h.shape
@@ -106,6 +114,17 @@ class RasodraInferenceModel(KVCacheInferenceMixin, RasodraForCausalLM):
                                        rope=rope, value_from_key=True, **paged)
         if T == 1:
             o = wa_ops.window_attention_decode(q[:, 0], ck, cv, q_start, m.scale, seq_ids=seq_ids, chunk=m.chunk, **paged)
+        elif self._chunks_as_batch(qk, m, T):
+            # prompts from position 0 whose length is a whole number of chunks (or one partial chunk): every chunk is an
+            # independent causal sequence, so the step runs on the tcgen05 flash-attention kernel with the chunks as
+            # batch rows; K comes back from the cache rows just written, V is the key columns of the projection output
+            size = m.chunk if (m.chunk and T > m.chunk) else T
+            lines = seq_ids.long() if seq_ids is not None else torch.arange(B, device=h.device)
+            kx = ck[lines, :, :T].transpose(1, 2).contiguous().reshape(B * (T // size), size, m.kv_heads, m.dim)
+            vx = qk[..., m.heads * m.dim:].reshape(B * (T // size), size, m.kv_heads, m.dim)
+            qx = q.reshape(B * (T // size), size, m.heads, m.dim)
+            o = attn_ops.flash_attn_func(qx.permute(0, 2, 1, 3), kx.permute(0, 2, 1, 3), vx.permute(0, 2, 1, 3),
+                                         softmax_scale=m.scale, causal=True).permute(0, 2, 1, 3)
         else:
             o = wa_ops.window_attention_prefill(q, ck, cv, q_start, m.scale, n_new=n_new, seq_ids=seq_ids, chunk=m.chunk,
                                                 **paged)
@@ -168,6 +187,9 @@ class RasodraInferenceModel(KVCacheInferenceMixin, RasodraForCausalLM):
                                      cfg.rms_norm_eps, False, dt)
         return mixer.o_proj(y.reshape(B, T, H * m.vdim))
 
+    CHUNKWISE_MIN_TOKENS = 64
+    CHUNKWISE_FP32 = False               # fp32 serving keeps the token-by-token scan (tests switch this on)
+
     def _mix_mlstm(self, i, mixer, h, q_start, n_new, seq_ids):
         m, cfg, dt = mixer.cfg, self.config, self.config.torch_dtype
         B, T, W = h.shape
@@ -175,8 +197,12 @@ class RasodraInferenceModel(KVCacheInferenceMixin, RasodraForCausalLM):
         st = self.kv_cache.state(i)
         proj = mixer.in_proj(h)
         gi, gf = mlstm_ops.mlstm_gates(h.reshape(N, W), mixer.gate_weight, mixer.gate_bias, H, m.gate_cap)
-        o = mlstm_ops.mlstm_scan(proj, (0, H * m.dim, 2 * H * m.dim), gi, gf, (st["S"], st["n"], st["m"]), q_start, H,
-                                 m.dim, m.vdim, m.dim ** -0.5, n_new=n_new, seq_ids=seq_ids)
+        # long bf16 steps take the chunk-wise form (matrix products); token generation, short steps and fp32 serving the
+        # token-by-token scan
+        chunkwise = T >= self.CHUNKWISE_MIN_TOKENS and (dt != torch.float32 or self.CHUNKWISE_FP32)
+        run = mlstm_ops.mlstm_chunkwise if chunkwise else mlstm_ops.mlstm_scan
+        o = run(proj, (0, H * m.dim, 2 * H * m.dim), gi, gf, (st["S"], st["n"], st["m"]), q_start, H, m.dim, m.vdim,
+                m.dim ** -0.5, n_new=n_new, seq_ids=seq_ids)
         y = mlstm_ops.head_norm_gate(o.reshape(N, H, m.vdim), proj.reshape(N, -1), 2 * H * m.dim + H * m.vdim, H, m.vdim,
                                      mixer.out_norm, cfg.rms_norm_eps, True, dt)
         return mixer.o_proj(y.reshape(B, T, H * m.vdim))

@@ -52,7 +52,8 @@ GROUPS["window_moe_serving"] = GROUPS["window_moe"] + [
 # the hybrid families (chunked / latent attention, recurrent matrix memory, dense feed-forward): the attention-over-cache
 # kernels, the norm kernels, their own two sources and the GEMM kernels behind the linear layers
 GROUPS["hybrid_serving"] = ["window_attention.cu", "post_norm.cu", "latent_attention.cu", "mlstm.cu", "runtime.cu",
-                            "gemm_tcgen05.cu", "gemm_smallm.cu", "fused_gemm_ar.cu", "tma_host.cu"]
+                            "gemm_tcgen05.cu", "gemm_smallm.cu", "fused_gemm_ar.cu", "tma_host.cu", "flash_attn_tc.cu",
+                            "attn_tc_host.cu"]
 
 # sources whose fp32 state is carried over thousands of steps: no approximate exp / tanh / division
 PRECISE_SOURCES = {"mlstm.cu"}

@@ -113,6 +113,119 @@ def mlstm_scan(proj: torch.Tensor, offsets: Tuple[int, int, int], gi: torch.Tens
     return out
 
 
+def _chunk_states(u, ftot, mloc, s0, m0, want_m: bool):
+    """The pass that is sequential over chunks (``csrc/mlstm.cu: mlstm_chunk_states_kernel``): ``u [BH, NC, E]`` becomes
+    the state at every chunk's start; returns ``(state after the last chunk [BH, E], m at chunk starts, m after)``."""
+    BH, NC, E = u.shape
+    s_out = torch.empty(BH, E, dtype=torch.float32, device=u.device)
+    m_start = torch.empty(BH, NC, dtype=torch.float32, device=u.device) if want_m else None
+    m_out = torch.empty(BH, dtype=torch.float32, device=u.device) if want_m else None
+    if u.is_cuda and _lib.available(GROUP):
+        L = _lib.lib(GROUP)
+        rc = L.nxd_mlstm_chunk_states(_lib.ptr(u), _lib.ptr(ftot), _lib.ptr(mloc), _lib.ptr(s0), _lib.ptr(m0),
+                                      _lib.ptr(s_out), _lib.ptr(m_start), _lib.ptr(m_out), _c.c_longlong(BH), _c.c_int(NC),
+                                      _c.c_longlong(E), _lib.stream_ptr())
+        _lib.check(rc, "nxd_mlstm_chunk_states", L)
+        return s_out, m_start, m_out
+    s, m = s0.clone(), m0.clone()
+    for c in range(NC):
+        mn = torch.maximum(ftot[:, c] + m, mloc[:, c])
+        a, b = torch.exp(ftot[:, c] + m - mn), torch.exp(mloc[:, c] - mn)
+        uc = u[:, c].clone()
+        u[:, c] = s
+        if want_m:
+            m_start[:, c] = m
+        s = a[:, None] * s + b[:, None] * uc
+        m = mn
+    s_out.copy_(s)
+    if want_m:
+        m_out.copy_(m)
+    return s_out, m_start, m_out
+
+
+NO_INPUT = -1e30         # log input gate of a padding token: it adds nothing and (with log forget gate 0) decays nothing
+
+
+def mlstm_chunkwise(proj: torch.Tensor, offsets: Tuple[int, int, int], gi: torch.Tensor, gf: torch.Tensor,
+                    state: Tuple[torch.Tensor, torch.Tensor, torch.Tensor], q_start: torch.Tensor, heads: int, dim: int,
+                    vdim: int, qscale: float, n_new: Optional[torch.Tensor] = None,
+                    seq_ids: Optional[torch.Tensor] = None, chunk: int = 64) -> torch.Tensor:
+    """``mlstm_scan`` for long steps, in chunk-wise form: same arguments, same result up to fp32 rounding.
+
+    With ``F_t`` the running sum of the log forget gates inside a chunk and ``(S_c, n_c, m_c)`` the state at its start,
+    ``m_t = F_t + max(m_c, max_{s<=t}(i_s - F_s))`` is exactly the running maximum of the token-by-token form, and
+
+        S_t^T q_t = exp(F_t + m_c - m_t) S_c^T q_t + sum_{s<=t} exp(F_t - F_s + i_s - m_t) (k_s . q_t) v_s
+
+    (``n_t . q_t`` likewise), so a chunk's outputs are four matrix products (q k^T, (q k^T * decay) v, q S_c, and
+    (k * w)^T v for the state) and every exponent is <= 0.  Only the walk over chunk states is sequential (one small
+    kernel).  Everything runs in fp32: the matrix products are fp32 library products, gates and state never leave fp32."""
+    B, T, _ = proj.shape
+    H, D, Dv, L = heads, dim, vdim, chunk
+    dev, f32 = proj.device, torch.float32
+    S, n, m = state
+    NC = (T + L - 1) // L
+    Tp = NC * L
+    cnt = n_new.long() if n_new is not None else torch.full((B,), T, device=dev, dtype=torch.long)
+    real = torch.arange(Tp, device=dev).reshape(1, Tp) < cnt.clamp(max=T).reshape(B, 1)            # [B, Tp]
+
+    def heads_of(off, width):                                      # -> [B, H, NC, L, width] fp32, padding rows zero
+        x = proj[..., off: off + H * width].to(f32).reshape(B, T, H, width)
+        if Tp != T:
+            x = torch.cat([x, x.new_zeros(B, Tp - T, H, width)], dim=1)
+        x = x * real.reshape(B, Tp, 1, 1)
+        return x.reshape(B, NC, L, H, width).permute(0, 3, 1, 2, 4)
+
+    q, k, v = heads_of(offsets[0], D) * qscale, heads_of(offsets[1], D), heads_of(offsets[2], Dv)
+
+    def gates_of(g, fill):                                         # [B*T, H] -> [B, H, NC, L]
+        g = g.reshape(B, T, H)
+        if Tp != T:
+            g = torch.cat([g, g.new_zeros(B, Tp - T, H)], dim=1)
+        g = torch.where(real.reshape(B, Tp, 1), g, torch.full_like(g, fill))
+        return g.reshape(B, NC, L, H).permute(0, 3, 1, 2)
+
+    fg, ig = gates_of(gf, 0.0), gates_of(gi, NO_INPUT)
+    F = torch.cumsum(fg, dim=-1)                                   # inclusive, inside the chunk
+    ftot = F[..., -1]                                              # [B, H, NC]
+    g = ig - F
+    gmax = g.max(dim=-1).values
+    mloc = ftot + gmax
+    # the chunk's own contribution to the state, relative to its local maximum
+    w = torch.exp(g - gmax.unsqueeze(-1))                          # [B, H, NC, L], <= 1
+    kw = k * w.unsqueeze(-1)
+    u = torch.matmul(kw.transpose(-1, -2), v).reshape(B * H, NC, D * Dv)
+    un = kw.sum(dim=-2).reshape(B * H, NC, D)
+    # state before the step: zero for rows that start a sequence, else what the line holds
+    lines = seq_ids.long() if seq_ids is not None else torch.arange(B, device=dev)
+    cont = (q_start.reshape(B) != 0).to(f32)
+    s0 = (S[lines] * cont.reshape(B, 1, 1, 1)).reshape(B * H, D * Dv)
+    n0 = (n[lines] * cont.reshape(B, 1, 1)).reshape(B * H, D)
+    m0 = (m[lines] * cont.reshape(B, 1)).reshape(B * H)
+    ft2, ml2 = ftot.reshape(B * H, NC).contiguous(), mloc.reshape(B * H, NC).contiguous()
+    s_end, m_start, m_end = _chunk_states(u, ft2, ml2, s0.contiguous(), m0.contiguous(), True)
+    n_end, _, _ = _chunk_states(un, ft2, ml2, n0.contiguous(), m0.contiguous(), False)
+    Sc, nc_, mc = u.reshape(B, H, NC, D, Dv), un.reshape(B, H, NC, D), m_start.reshape(B, H, NC)
+    # outputs of every chunk
+    m_t = F + torch.maximum(mc.unsqueeze(-1), torch.cummax(g, dim=-1).values)                      # [B, H, NC, L]
+    causal = torch.ones(L, L, dtype=torch.bool, device=dev).tril()
+    expo = (F - m_t).unsqueeze(-1) + g.unsqueeze(-2)                                               # [.., t, s]
+    decay = torch.exp(expo.masked_fill(~causal, float("-inf")))
+    P = torch.matmul(q, k.transpose(-1, -2)) * decay
+    inter = torch.exp(F + mc.unsqueeze(-1) - m_t)                                                  # [B, H, NC, L]
+    num = torch.matmul(P, v) + inter.unsqueeze(-1) * torch.matmul(q, Sc)
+    nq = P.sum(dim=-1) + inter * (q * nc_.unsqueeze(-2)).sum(dim=-1)
+    den = torch.maximum(nq.abs(), torch.exp(-m_t)) + DENOMINATOR_FLOOR
+    out = (num / den.unsqueeze(-1)).permute(0, 2, 3, 1, 4).reshape(B, Tp, H, Dv)[:, :T]
+    out = out * real[:, :T].reshape(B, T, 1, 1)
+    # rows with no real token keep their state (blended by the row mask on the device: no host read)
+    kf = (cnt > 0).to(f32)
+    S[lines] = s_end.reshape(B, H, D, Dv) * kf.reshape(B, 1, 1, 1) + S[lines] * (1 - kf).reshape(B, 1, 1, 1)
+    n[lines] = n_end.reshape(B, H, D) * kf.reshape(B, 1, 1) + n[lines] * (1 - kf).reshape(B, 1, 1)
+    m[lines] = m_end.reshape(B, H) * kf.reshape(B, 1) + m[lines] * (1 - kf).reshape(B, 1)
+    return out.contiguous()
+
+
 def head_norm_gate(o: torch.Tensor, gate_src: torch.Tensor, gate_offset: int, heads: int, vdim: int,
                    weight: Optional[torch.Tensor], eps: float, normalize: bool, out_dtype: torch.dtype) -> torch.Tensor:
     """``o [N, heads, vdim]`` -> ``[N, heads * vdim]`` in ``out_dtype``: every head divided by its root mean square

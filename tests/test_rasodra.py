@@ -104,12 +104,19 @@ def replay(model, steps):
 
 
 def check_rows(rows, ref, places, dt):
+    """Every position against the oracle: centred difference over the vocabulary, relative to the spread of the logits.
+    fp32 is strict.  bf16 rounding through six tiny layers reaches a few percent at single positions (the PyTorch bf16
+    path of the same ops shows the same), so bf16 bounds every position at 0.12 and the mean over positions at 0.04; a
+    wrong key, edge or state moves positions by far more."""
     assert len(rows) == len(places)
+    rels = []
     for row, p in zip(rows, places):
         d = row.to(F64) - ref[p]
         d = d - d.mean()
         rel = float(d.pow(2).mean().sqrt() / ref[p].std())
-        assert rel <= (2e-4 if dt == torch.float32 else 4e-2), f"position {p}: relative error {rel:.2e}"
+        assert rel <= (2e-4 if dt == torch.float32 else 0.12), f"position {p}: relative error {rel:.2e}"
+        rels.append(rel)
+    assert dt == torch.float32 or sum(rels) / len(rels) <= 0.04, f"mean relative error {sum(rels) / len(rels):.2e}"
 
 
 # ---- mechanisms alone ---------------------------------------------------------------------------------------------------
@@ -290,6 +297,28 @@ def test_recurrent_gates_scan_and_state(dev, dt):
     close(torch.cat(got), ref, torch.float32, scale=5.0)
     for a, b in zip(st, st2):
         close(a[2], b[2].to("cpu", F64), torch.float32, scale=5.0)
+    # the chunk-wise form: the whole prompt with chunks of 8 (five full chunks and a partial one), then two portions that
+    # continue from the line's state, the second with padding behind it; same outputs, same final state
+    st3 = state(fill=5.0)
+    cw = ml.mlstm_chunkwise(proj[None].to(dev).contiguous(), offs, gi, gf, st3, torch.tensor([0], device=dev), H, D, Dv,
+                            D ** -0.5, seq_ids=line, chunk=8)
+    close(cw[0], ref, torch.float32, scale=5.0)
+    for a, b in zip(st, st3):
+        close(a[2], b[2].to("cpu", F64), torch.float32, scale=5.0)
+    assert float((st3[0][0] - 5.0).abs().max()) == 0.0
+    st4 = state(fill=1.0)
+    first = ml.mlstm_chunkwise(proj[None, :19].to(dev).contiguous(), offs, gi[:19], gf[:19], st4,
+                               torch.tensor([0], device=dev), H, D, Dv, D ** -0.5, seq_ids=line, chunk=16)
+    part = torch.zeros(1, 30, proj.shape[1], dtype=dt)
+    part[0, :26] = proj[19:]
+    g_i, g_f = torch.zeros(30, H), torch.zeros(30, H)
+    g_i[:26], g_f[:26] = gi[19:].cpu(), gf[19:].cpu()
+    second = ml.mlstm_chunkwise(part.to(dev), offs, g_i.to(dev), g_f.to(dev), st4, torch.tensor([19], device=dev), H, D,
+                                Dv, D ** -0.5, n_new=torch.tensor([26], device=dev), seq_ids=line, chunk=16)
+    close(torch.cat([first[0], second[0, :26]]), ref, torch.float32, scale=5.0)
+    assert float(second[0, 26:].abs().sum()) == 0.0
+    for a, b in zip(st, st4):
+        close(a[2], b[2].to("cpu", F64), torch.float32, scale=5.0)
 
 
 @case
@@ -397,6 +426,24 @@ def test_unequal_batch_equals_each_alone_and_lines_are_reused(dev, dt):
         check_rows(got[k], ref[k], [lens[k] - 1, lens[k], lens[k] + 1, lens[k] + 2], dt)
     for k in "de":
         check_rows(got[k], ref[k], [0, lens[k] - 1] + [lens[k] + s for s in range(6)], dt)
+
+
+@case
+def test_long_prompt_steps_take_the_chunkwise_recurrence(dev, dt):
+    """Steps of 64+ tokens run the recurrent layers in chunk-wise form (bf16 serving; forced here for fp32 too): a prompt
+    of 150 tokens in two portions next to a short request, then decoding from the state they leave."""
+    cfg = config(layers=[layer("mlstm", mlp=None), layer("mlstm"), layer("latent_attention", mlp=None)])
+    model, sd = build(cfg, dev, dt, lines=2, seq_len=200)
+    model.CHUNKWISE_FP32 = True
+    a, b = tokens_of(cfg, 160, 31), tokens_of(cfg, 75, 32)
+    ra, rb = O.forward(cfg, sd, a), O.forward(cfg, sd, b)
+    steps = [([{"id": "a", "tokens": a[:80], "want": [0, 63, 64, 79]}, {"id": "b", "tokens": b[:70], "want": [69]}], []),
+             ([{"id": "a", "tokens": a[80:150], "want": [0, 69]}], [])]
+    steps += [([{"id": "a", "tokens": [a[150 + s]], "want": [0]}, {"id": "b", "tokens": [b[70 + s]], "want": [0]}], [])
+              for s in range(5)]
+    got = replay(model, steps)
+    check_rows(got["a"], ra, [0, 63, 64, 79, 80, 149] + list(range(150, 155)), dt)
+    check_rows(got["b"], rb, [69] + list(range(70, 75)), dt)
 
 
 @case

@@ -34,25 +34,44 @@ template <typename T>
 __global__ void mlstm_gates_kernel(const T* __restrict__ h, const T* __restrict__ w, const float* __restrict__ bias,
                                    float* __restrict__ gi, float* __restrict__ gf, long long units, int W, int H,
                                    float cap) {
+    // one warp per token: the input row is read once (held in registers in pieces of 32 * GX values), the 2 * H gate
+    // rows come from L1 / L2
+    constexpr int GX = 8;
     const int lane = threadIdx.x & 31;
-    const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (unit >= units) return;
-    const long long n = unit / H;
-    const int hd = (int)(unit % H);
+    const long long n = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (n >= units) return;
     const T* x = h + n * W;
-    const T* wi = w + (long long)hd * W;
-    const T* wf = w + (long long)(H + hd) * W;
-    float si = 0.f, sf = 0.f;
-    for (int c = lane; c < W; c += 32) {
-        const float xv = ldf(x + c);
-        si = fmaf(xv, ldf(wi + c), si);
-        sf = fmaf(xv, ldf(wf + c), sf);
-    }
-    si = warp_sum(si);
-    sf = warp_sum(sf);
-    if (lane == 0) {
-        gi[unit] = soft_cap(si + bias[hd], cap);
-        gf[unit] = log_sigmoid(soft_cap(sf + bias[H + hd], cap));
+    for (int r0 = 0; r0 < 2 * H; r0 += 4) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int c0 = 0; c0 < W; c0 += 32 * GX) {
+            float xv[GX];
+#pragma unroll
+            for (int j = 0; j < GX; ++j) {
+                const int c = c0 + j * 32 + lane;
+                xv[j] = c < W ? ldf(x + c) : 0.f;
+            }
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                if (r0 + r < 2 * H) {
+                    const T* wr = w + (long long)(r0 + r) * W;
+#pragma unroll
+                    for (int j = 0; j < GX; ++j) {
+                        const int c = c0 + j * 32 + lane;
+                        if (c < W) acc[r] = fmaf(xv[j], ldf(wr + c), acc[r]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const float sum = warp_sum(acc[r]);
+            const int row = r0 + r;
+            if (lane == 0 && row < 2 * H) {
+                const float pre = soft_cap(sum + bias[row], cap);
+                if (row < H) gi[n * H + row] = pre;
+                else gf[n * H + row - H] = log_sigmoid(pre);
+            }
+        }
     }
 }
 
@@ -293,13 +312,28 @@ __global__ void relu_squared_kernel(const T* __restrict__ x, T* __restrict__ y, 
     }
 }
 
+// bf16, 8 values (16 bytes) per thread; n8 = n / 8 full vectors, the tail goes through the scalar kernel
+__global__ void relu_squared_vec_kernel(const bf16x8* __restrict__ x, bf16x8* __restrict__ y, long long n8) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n8) {
+        float f[8];
+        unpack8(x[i], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float v = fmaxf(f[j], 0.f);
+            f[j] = v * v;
+        }
+        y[i] = pack8(f);
+    }
+}
+
 }  // namespace
 
 // dtype (mixer input and gate rows): 0 = bf16, 1 = fp32
 NXD_API int nxd_mlstm_gates(int dtype, const void* h, const void* w, const float* bias, float* gi, float* gf,
                             long long N, int W, int H, float cap, void* stream) {
-    const long long units = N * H;
-    if (units == 0) return 0;
+    const long long units = N;
+    if (units == 0 || H == 0) return 0;
     const int wpb = 8;
     const unsigned blocks = (unsigned)((units + wpb - 1) / wpb);
     cudaStream_t st = (cudaStream_t)stream;
@@ -356,7 +390,15 @@ NXD_API int nxd_head_norm_gate(int o_dtype, int dtype, const void* o, const void
 NXD_API int nxd_relu_squared(int dtype, const void* x, void* y, long long n, void* stream) {
     if (n == 0) return 0;
     const unsigned blocks = (unsigned)((n + 255) / 256);
-    if (dtype == 0)
+    if (dtype == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)y % 16) == 0 && n >= 8) {
+        const long long n8 = n / 8;
+        relu_squared_vec_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const bf16x8*)x, (bf16x8*)y,
+                                                                                               n8);
+        NXD_LAUNCH_CHECK();
+        if (n8 * 8 == n) return 0;
+        const long long rest = n - n8 * 8;
+        relu_squared_kernel<bf16><<<1, 256, 0, (cudaStream_t)stream>>>((const bf16*)x + n8 * 8, (bf16*)y + n8 * 8, rest);
+    } else if (dtype == 0)
         relu_squared_kernel<bf16><<<blocks, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)y, n);
     else
         relu_squared_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((const float*)x, (float*)y, n);

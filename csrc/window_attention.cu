@@ -604,14 +604,18 @@ window_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ cache_k
 // each of the four warps takes 16 rows of a tile and keeps its own online-softmax state, merged through shared memory.
 constexpr int DM_THREADS = 128, DM_ROWS = 16;
 
-template <int D, int DV>
+// VS: value columns per CTA.  A wide value row (the latent rows of a compressed key/value projection) is split over
+// gridDim.z CTAs: each recomputes the scores of its 16 query heads and accumulates its own VS output columns, so the
+// accumulator stays in registers; the other slices' reads of the same key rows hit L2.  QS: the query fragments are
+// re-read from shared memory at every step of the key dimension instead of living in registers (large D).
+template <int D, int DV, int VS, bool QS>
 __global__ void __launch_bounds__(DM_THREADS)
 window_attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache_k,
                               const bf16* __restrict__ cache_v, CacheAddr ka, CacheAddr va, bf16* __restrict__ out,
                               const int* __restrict__ positions, const int* __restrict__ seq_ids,
                               const float* __restrict__ slopes, int H, int G, float scale, int window, int keep_first,
                               int chunk, const float* __restrict__ sinks, int groups_per_kv) {
-    constexpr int LDK = D + 8, LDV = DV + 8, CK = D / 8, CV = DV / 8;
+    constexpr int LDK = D + 8, LDV = VS + 8, CK = D / 8, CV = VS / 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);       // [DM_ROWS][LDK]
     bf16* Ks = Qs + DM_ROWS * LDK;                      // [2][MK][LDK]
@@ -622,6 +626,7 @@ window_attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict
     const int R_all = H / G;
     const int g = blockIdx.x / groups_per_kv, r_base = (blockIdx.x % groups_per_kv) * DM_ROWS;
     const int b = blockIdx.y;
+    const int vz = blockIdx.z * VS;                       // first value column of this CTA
     const int R = min(DM_ROWS, R_all - r_base);
     const int h0 = g * R_all + r_base;
     const int p = positions[b];
@@ -661,7 +666,7 @@ window_attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict
         for (int idx = tid; idx < MK * CV; idx += DM_THREADS) {
             const int r = idx / CV, c = idx - r * CV;
             const bool ok = voff[buf][r] >= 0;
-            mma::cp_async16(vs_addr + ((buf * MK + r) * LDV + c * 8) * 2, ok ? cache_v + voff[buf][r] + c * 8 : cache_v, ok);
+            mma::cp_async16(vs_addr + ((buf * MK + r) * LDV + c * 8) * 2, ok ? cache_v + voff[buf][r] + vz + c * 8 : cache_v, ok);
         }
         mma::cp_async_commit();
     };
@@ -674,10 +679,10 @@ window_attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict
     const float sl0 = (slopes != nullptr && ok0 ? slopes[h0 + r_lo] : 0.f) * LOG2E;
     const float sl1 = (slopes != nullptr && ok1 ? slopes[h0 + r_lo + 8] : 0.f) * LOG2E;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-    float o[DV / 8][4];
+    float o[VS / 8][4];
 #pragma unroll
-    for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    uint32_t qf[D / 16][4];
+    for (int i = 0; i < VS / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    uint32_t qf[QS ? 1 : D / 16][4];
 
     for (int n = 0; n < n_tiles; ++n) {
         const int buf = n & 1;
@@ -688,9 +693,9 @@ window_attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict
             mma::cp_async_wait<0>();
         }
         __syncthreads();
-        if (n == 0) {
+        if (!QS && n == 0) {
 #pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk)
+            for (int kk = 0; kk < (QS ? 1 : D / 16); ++kk)
                 mma::ldsm_x4(qf[kk], qs_addr + ((lane & 15) * LDK + kk * 16 + (lane >> 4) * 8) * 2);
         }
         const int kt = n < n_sink_tiles ? n : t_win + (n - n_sink_tiles);
@@ -703,8 +708,9 @@ window_attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict
             uint32_t bfr[4];
             const int row = warp * 16 + (lane & 7) + (lane >> 4) * 8;
             mma::ldsm_x4(bfr, kb_addr + (row * LDK + kk * 16 + ((lane >> 3) & 1) * 8) * 2);
-            mma::mma16816(s[0], qf[kk], bfr[0], bfr[1]);
-            mma::mma16816(s[1], qf[kk], bfr[2], bfr[3]);
+            if (QS) mma::ldsm_x4(qf[0], qs_addr + ((lane & 15) * LDK + kk * 16 + (lane >> 4) * 8) * 2);
+            mma::mma16816(s[0], qf[QS ? 0 : kk], bfr[0], bfr[1]);
+            mma::mma16816(s[1], qf[QS ? 0 : kk], bfr[2], bfr[3]);
         }
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -746,7 +752,7 @@ window_attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict
         pa[3] = mma::pack2(s[1][2], s[1][3]);
         const uint32_t vb_addr = vs_addr + buf * MK * LDV * 2;
 #pragma unroll
-        for (int dj = 0; dj < DV / 16; ++dj) {
+        for (int dj = 0; dj < VS / 16; ++dj) {
             uint32_t bfr[4];
             const int row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
             mma::ldsm_x4_t(bfr, vb_addr + (row * LDV + dj * 16 + (lane >> 4) * 8) * 2);
@@ -767,12 +773,12 @@ window_attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict
     l0 = mma::quad_sum(l0);
     l1 = mma::quad_sum(l1);
     float* Ms = reinterpret_cast<float*>(smem_raw);
-    constexpr int MS = DV + 2;
+    constexpr int MS = VS + 2;
     {
         float* d0 = Ms + ((warp * DM_ROWS) + r_lo) * MS;
         float* d1 = d0 + 8 * MS;
 #pragma unroll
-        for (int i = 0; i < DV / 8; ++i) {
+        for (int i = 0; i < VS / 8; ++i) {
             const int c = i * 8 + (lane & 3) * 2;
             d0[c] = o[i][0];
             d0[c + 1] = o[i][1];
@@ -780,40 +786,41 @@ window_attn_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict
             d1[c + 1] = o[i][3];
         }
         if ((lane & 3) == 0) {
-            d0[DV] = m0;
-            d0[DV + 1] = l0;
-            d1[DV] = m1;
-            d1[DV + 1] = l1;
+            d0[VS] = m0;
+            d0[VS + 1] = l0;
+            d1[VS] = m1;
+            d1[VS + 1] = l1;
         }
     }
     __syncthreads();
-    for (int idx = tid; idx < R * DV; idx += DM_THREADS) {
-        const int r = idx / DV, c = idx - r * DV;
+    for (int idx = tid; idx < R * VS; idx += DM_THREADS) {
+        const int r = idx / VS, c = idx - r * VS;
         float mx = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) mx = fmaxf(mx, Ms[(w * DM_ROWS + r) * MS + DV]);
+        for (int w = 0; w < 4; ++w) mx = fmaxf(mx, Ms[(w * DM_ROWS + r) * MS + VS]);
         float num = 0.f, den = 0.f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const float* src = Ms + (w * DM_ROWS + r) * MS;
-            const float f = src[DV] == -INFINITY ? 0.f : exp2f(src[DV] - mx);
+            const float f = src[VS] == -INFINITY ? 0.f : exp2f(src[VS] - mx);
             num = fmaf(f, src[c], num);
-            den = fmaf(f, src[DV + 1], den);
+            den = fmaf(f, src[VS + 1], den);
         }
         if (sinks != nullptr) den += exp2f(sinks[h0 + r] * LOG2E - (mx == -INFINITY ? 0.f : mx));
-        out[((long long)b * H + h0 + r) * DV + c] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+        out[((long long)b * H + h0 + r) * DV + vz + c] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
     }
 }
 
-template <int D, int DV>
+template <int D, int DV, int VS = DV>
 int launch_decode_mma(const void* q, const void* ck, const void* cv, CacheAddr ka, CacheAddr va, void* out,
                       const int* positions, const int* seq_ids, const float* slopes, int B, int H, int G, float scale,
                       int window, int keep_first, int chunk, const float* sinks, cudaStream_t st) {
     const int groups = (H / G + DM_ROWS - 1) / DM_ROWS;
-    const size_t smem = (size_t)(DM_ROWS * (D + 8) + 2 * MK * (D + 8) + 2 * MK * (DV + 8)) * sizeof(bf16);
-    auto kern = window_attn_decode_mma_kernel<D, DV>;
+    static_assert(DV % VS == 0 && VS % 16 == 0, "value slices");
+    const size_t smem = (size_t)(DM_ROWS * (D + 8) + 2 * MK * (D + 8) + 2 * MK * (VS + 8)) * sizeof(bf16);
+    auto kern = window_attn_decode_mma_kernel<D, DV, VS, (D > 256)>;
     if (smem > 48 * 1024) NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    dim3 grid(G * groups, B);
+    dim3 grid(G * groups, B, DV / VS);
     kern<<<grid, DM_THREADS, smem, st>>>((const bf16*)q, (const bf16*)ck, (const bf16*)cv, ka, va, (bf16*)out, positions,
                                          seq_ids, slopes, H, G, scale, window, keep_first, chunk, sinks, groups);
     NXD_LAUNCH_CHECK();
@@ -1008,8 +1015,13 @@ NXD_API int nxd_masked_attn_decode(int dtype, const void* q, const void* cache_k
         NXD_WD_CASE(64, 128);
         NXD_WD_CASE(128, 64);
         NXD_WD_CASE(160, 128);    // latent rows: compressed key/value + shared rotated key part; value = the compressed part
-        NXD_WD_CASE(288, 256);
 #undef NXD_WD_CASE
+        if (D == 288 && Dv == 256)                   // wide latent rows: the value columns are split over CTAs
+            return launch_decode_mma<288, 256, 128>(q, cache_k, cache_v, ka, va, out, positions, seq_ids, slopes, B, H, G,
+                                                    scale, window, keep_first, chunk, sinks, st);
+        if (D == 576 && Dv == 512)
+            return launch_decode_mma<576, 512, 128>(q, cache_k, cache_v, ka, va, out, positions, seq_ids, slopes, B, H, G,
+                                                    scale, window, keep_first, chunk, sinks, st);
     }
     NXD_REQUIRE(impl != 2, "attention decode: no tensor-core kernel for bf16=%d D=%d Dv=%d", dtype == 0, D, Dv);
     if (dtype == 0)

@@ -214,7 +214,9 @@ class RasodraInferenceModel(KVCacheInferenceMixin, RasodraForCausalLM):
         dt = self.config.torch_dtype
         x = hidden if hidden.is_contiguous() else hidden.contiguous()
         h = residual if residual is not None else layer.norm1(x, out_dtype=dt)
-        q_start = positions[:, 0]
+        if "q_start" not in self._step_kv:      # one int32 copy of the rows' first positions per step, not per kernel
+            self._step_kv["q_start"] = positions[:, 0].to(torch.int32).contiguous()
+        q_start = self._step_kv["q_start"]
         n_new = self._step_new_tokens if prefill else None
         y = self._MIX[layer.type](self, i, layer.mixer, h, q_start, n_new, seq_ids)
         nxt = self._sequence[i + 1].norm1 if i + 1 < len(self._sequence) else None

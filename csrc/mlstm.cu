@@ -221,16 +221,24 @@ __global__ void mlstm_chunk_states_kernel(float* __restrict__ u, const float* __
     if (e >= E) return;
     float s = s0[bh * E + e];
     float m = m0[bh];
-    for (int c = 0; c < NC; ++c) {
-        const float ft = ftot[bh * NC + c], ml = mloc[bh * NC + c];
-        const float mn = fmaxf(ft + m, ml);
-        const float a = expf(ft + m - mn), b = expf(ml - mn);
-        float* up = u + (bh * NC + c) * E + e;
-        const float uv = *up;
-        *up = s;
-        if (e == 0 && m_start != nullptr) m_start[bh * NC + c] = m;
-        s = fmaf(a, s, b * uv);
-        m = mn;
+    constexpr int AHEAD = 8;                  // loads of the next chunks are issued before the stores of these
+    for (int c0 = 0; c0 < NC; c0 += AHEAD) {
+        float uv[AHEAD];
+#pragma unroll
+        for (int j = 0; j < AHEAD; ++j) uv[j] = c0 + j < NC ? u[(bh * NC + c0 + j) * E + e] : 0.f;
+#pragma unroll
+        for (int j = 0; j < AHEAD; ++j) {
+            const int c = c0 + j;
+            if (c < NC) {
+                const float ft = ftot[bh * NC + c], ml = mloc[bh * NC + c];
+                const float mn = fmaxf(ft + m, ml);
+                const float a = expf(ft + m - mn), b = expf(ml - mn);
+                u[(bh * NC + c) * E + e] = s;
+                if (e == 0 && m_start != nullptr) m_start[bh * NC + c] = m;
+                s = fmaf(a, s, b * uv[j]);
+                m = mn;
+            }
+        }
     }
     s_out[bh * E + e] = s;
     if (e == 0 && m_out != nullptr) m_out[bh] = m;

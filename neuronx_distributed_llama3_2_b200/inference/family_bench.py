@@ -306,6 +306,14 @@ def hybrid_kernel_cases(s: dict, steps: int, warmup: int, dev) -> List[dict]:
     cv = torch.randn(max(B, Bd), G, S, D, device=dev, dtype=bf)
     ms = timer(lambda: wa.window_attention_prefill(q, ck, cv, zero, D ** -0.5, chunk=s["chunk"]), steps, warmup)
     row("chunked attention prefill (mma.sync, over the cache)", "prefill attention", ms, flops=4.0 * D * pairs_chunk * H * B)
+    if T % s["chunk"] == 0:
+        nch, size = T // s["chunk"], s["chunk"]
+        qx = q.reshape(B * nch, size, H, D).permute(0, 2, 1, 3)
+        kx = ck[:B, :, :T].transpose(1, 2).contiguous().reshape(B * nch, size, G, D).permute(0, 2, 1, 3)
+        vx = cv[:B, :, :T].transpose(1, 2).contiguous().reshape(B * nch, size, G, D).permute(0, 2, 1, 3)
+        ms = timer(lambda: attn_ops.flash_attn_func(qx, kx, vx, softmax_scale=D ** -0.5, causal=True), steps, warmup)
+        row("chunked attention prefill (tcgen05, chunks as batch rows: prompts from position 0)", "prefill attention", ms,
+            flops=4.0 * D * pairs_chunk * H * B)
     qh, kh, vh = q.permute(0, 2, 1, 3), ck[:B, :, :T], cv[:B, :, :T]
     ms = timer(lambda: attn_ops.flash_attn_func(qh, kh, vh, causal=True), steps, warmup)
     row("flash attention forward (tcgen05, plain causal)", "prefill attention", ms, flops=4.0 * D * pairs_causal * H * B)
@@ -351,8 +359,12 @@ def hybrid_kernel_cases(s: dict, steps: int, warmup: int, dev) -> List[dict]:
     gf = -torch.rand(B * T, Hr, device=dev) * 0.1
     st = (torch.zeros(Bd, Hr, Dk, Dvr, device=dev), torch.zeros(Bd, Hr, Dk, device=dev), torch.zeros(Bd, Hr, device=dev))
     ms = timer(lambda: ml.mlstm_scan(pr, (0, Hr * Dk, 2 * Hr * Dk), gi, gf, st, zero, Hr, Dk, Dvr, Dk ** -0.5), steps, warmup)
-    row("recurrent scan, prompt (token by token in registers)", "prefill attention", ms,
-        flops=6.0 * Dk * Dvr * Hr * B * T)
+    row("recurrent scan, prompt (token by token in registers; fp32 serving, short steps)", "prefill attention", ms,
+        flops=4.0 * Dk * Dvr * Hr * B * T)
+    ms = timer(lambda: ml.mlstm_chunkwise(pr, (0, Hr * Dk, 2 * Hr * Dk), gi, gf, st, zero, Hr, Dk, Dvr, Dk ** -0.5), steps,
+               warmup)
+    row("recurrent prompt, chunk-wise (fp32 matrix products; bf16 serving, steps of 64+ tokens)", "prefill attention", ms,
+        flops=4.0 * Dk * Dvr * Hr * B * T)
     prd = torch.randn(Bd, 1, ld, device=dev, dtype=bf) * 0.3
     one = torch.ones(Bd, dtype=torch.int32, device=dev)
     ms = timer(lambda: ml.mlstm_scan(prd, (0, Hr * Dk, 2 * Hr * Dk), gi[:Bd], gf[:Bd], st, one, Hr, Dk, Dvr, Dk ** -0.5),

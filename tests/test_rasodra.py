@@ -172,13 +172,14 @@ def _attention_oracle(q, k, v, q_pos, scale, chunk=None, sink=None):
 
 @case
 @pytest.mark.parametrize("paged", [False, True], ids=["contiguous", "paged"])
-@pytest.mark.parametrize("chunk,sink", [(8, False), (5, True), (None, True), (64, False)])
-def test_attention_over_the_cache_chunks_and_sinks(dev, dt, paged, chunk, sink):
+@pytest.mark.parametrize("D", [16, 32, 64], ids=["d16", "d32", "d64"])
+@pytest.mark.parametrize("chunk,sink", [(8, False), (5, True), (None, True), (64, False), (48, True), (100, False)])
+def test_attention_over_the_cache_chunks_and_sinks(dev, dt, paged, chunk, sink, D):
     """Prompt portion at an offset and single-token decoding; one key just inside and one just outside the query's chunk
     carry a score that dominates, so a chunk edge that is one token off changes the result."""
     torch.manual_seed(3)
-    H, G, D, Dv, S, page = 4, 2, 16, 16, 80, 8
-    start, T = 37, 21
+    H, G, Dv, S, page = 4, 2, D, 160, 8                 # head sizes 32 and 64 take the tensor-core kernels in bf16
+    start, T = 101, 37
     n_ctx = start + T
     k = torch.randn(G, n_ctx, D).to(dt)
     v = torch.randn(G, n_ctx, Dv).to(dt)
@@ -190,8 +191,9 @@ def test_attention_over_the_cache_chunks_and_sinks(dev, dt, paged, chunk, sink):
             k[:, edge - 1] = q[T - 1, 0] * 3.0                       # just outside: must not be seen
     sinks = torch.tensor([0.5, -1.0, 3.0, 6.0]) if sink else None
     if paged:
-        table = torch.tensor([[5, 2, 9, 0, 7, 1, 8, 3, 6, 4], [11, 12, 13, 14, 15, 16, 17, 18, 19, 10]], dtype=torch.int32)
-        ck, cv = torch.zeros(20, G, page, D, dtype=dt), torch.zeros(20, G, page, Dv, dtype=dt)
+        g = torch.Generator().manual_seed(5)
+        table = torch.randperm(40, generator=g).to(torch.int32).reshape(2, 20)
+        ck, cv = torch.zeros(40, G, page, D, dtype=dt), torch.zeros(40, G, page, Dv, dtype=dt)
         for pos in range(n_ctx):
             ck[table[1, pos // page], :, pos % page], cv[table[1, pos // page], :, pos % page] = k[:, pos], v[:, pos]
         kw = dict(block_table=table.to(dev), page_size=page)
@@ -201,16 +203,17 @@ def test_attention_over_the_cache_chunks_and_sinks(dev, dt, paged, chunk, sink):
         kw = {}
     ck, cv = ck.to(dev), cv.to(dev)
     sk = sinks.to(dev) if sink else None
-    ref = _attention_oracle(q, k, v, torch.arange(start, n_ctx), 0.3, chunk, sinks)
+    scale = 0.3 * (16 / D) ** 0.5
+    ref = _attention_oracle(q, k, v, torch.arange(start, n_ctx), scale, chunk, sinks)
     line = torch.tensor([1], dtype=torch.int32, device=dev)
-    out = wa.window_attention_prefill(q[None].to(dev), ck, cv, torch.tensor([start], device=dev), 0.3, seq_ids=line,
+    out = wa.window_attention_prefill(q[None].to(dev), ck, cv, torch.tensor([start], device=dev), scale, seq_ids=line,
                                       chunk=chunk, sinks=sk, **kw)
     close(out[0], ref, dt)
-    one = wa.window_attention_decode(q[T - 1:T].to(dev), ck, cv, torch.tensor([n_ctx - 1], device=dev), 0.3, seq_ids=line,
-                                     chunk=chunk, sinks=sk, **kw)
+    one = wa.window_attention_decode(q[T - 1:T].to(dev), ck, cv, torch.tensor([n_ctx - 1], device=dev), scale,
+                                     seq_ids=line, chunk=chunk, sinks=sk, **kw)
     close(one[0], ref[T - 1], dt)
     if chunk and edge >= 1:
-        seen_outside = _attention_oracle(q[T - 1:], k, v, torch.tensor([n_ctx - 1]), 0.3, None, sinks)
+        seen_outside = _attention_oracle(q[T - 1:], k, v, torch.tensor([n_ctx - 1]), scale, None, sinks)
         assert float((seen_outside[0] - ref[T - 1]).abs().max()) > 0.05
 
 
@@ -466,6 +469,31 @@ def test_long_prompt_steps_take_the_chunkwise_recurrence(dev, dt):
     got = replay(model, steps)
     check_rows(got["a"], ra, [0, 63, 64, 79, 80, 149] + list(range(150, 155)), dt)
     check_rows(got["b"], rb, [69] + list(range(70, 75)), dt)
+
+
+@case
+def test_tensor_core_head_sizes_through_the_model(dev, dt):
+    """Head sizes that the bf16 serving path runs on its tensor-core kernels: chunked attention with heads of 64 (prompts
+    of a whole number of chunks run with the chunks as batch rows of the flash-attention kernel, other lengths and
+    portions over the cache), latent attention with expanded heads of 96 | 64 and latent rows of 160 columns."""
+    att = layer("attention", mlp=None, heads=2, kv_heads=1, dim=64, vdim=64, scale=0.125, mask={"size": 64},
+                rot={"dims": 32, "base": 10000.0})
+    lat = layer("latent_attention", mlp=None, heads=2, dim=64, rot_dim=32, vdim=64, kv_rank=128, scale=0.1,
+                rot={"dims": 32, "base": 10000.0})
+    cfg = config(layers=[att, lat, dict(att, weights_of=0)], width=64, vocab=80)
+    model, sd = build(cfg, dev, dt, lines=3, seq_len=260)
+    a, b, c = tokens_of(cfg, 200, 51), tokens_of(cfg, 140, 52), tokens_of(cfg, 230, 53)
+    ra, rb, rc = (O.forward(cfg, sd, t) for t in (a, b, c))
+    steps = [([{"id": "a", "tokens": a[:192], "want": [0, 63, 64, 127, 128, 191]},          # 3 chunks; b is padded to 192
+               {"id": "b", "tokens": b[:130], "want": [64, 129]}], []),
+             ([{"id": "c", "tokens": c[:150], "want": [149]}], []),                         # not a whole number of chunks
+             ([{"id": "c", "tokens": c[150:220], "want": [0, 41, 42, 69]}], [])]            # a portion at an offset
+    steps += [([{"id": "a", "tokens": [a[192 + s]], "want": [0]}, {"id": "b", "tokens": [b[130 + s]], "want": [0]},
+                {"id": "c", "tokens": [c[220 + s]], "want": [0]}], []) for s in range(8)]
+    got = replay(model, steps)
+    check_rows(got["a"], ra, [0, 63, 64, 127, 128, 191] + list(range(192, 200)), dt)
+    check_rows(got["b"], rb, [64, 129] + list(range(130, 138)), dt)
+    check_rows(got["c"], rc, [149, 150, 191, 192, 219] + list(range(220, 228)), dt)
 
 
 @case

@@ -196,6 +196,65 @@ mlstm_scan_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_off
     }
 }
 
+// One token per row (token generation): nothing is carried in registers between tokens, so the mapping is chosen for the
+// state traffic alone -- a lane owns a value column (a warp reads 128 contiguous bytes of a state row), the four warps
+// take every fourth row, partial sums meet in shared memory.  Any key size.
+template <typename T>
+__global__ void __launch_bounds__(128)
+mlstm_step_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_off, int v_off, const float* __restrict__ gi,
+                  const float* __restrict__ gf, float* __restrict__ state_s, const float* __restrict__ state_n,
+                  const float* __restrict__ state_m, float* __restrict__ next_n, float* __restrict__ next_m,
+                  float* __restrict__ out, const int* __restrict__ q_start, const int* __restrict__ seq_ids, int H, int D,
+                  int Dv, float qscale) {
+    extern __shared__ float smem[];
+    float* qs = smem;                         // [D]
+    float* ks = qs + D;                       // [D]
+    __shared__ float red[4][32];
+    __shared__ float rednq[4];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int col = blockIdx.x * 32 + lane, hd = blockIdx.y, b = blockIdx.z;
+    const bool col_ok = col < Dv;
+    const int line = seq_ids != nullptr ? seq_ids[b] : b;
+    const bool fresh = q_start[b] == 0;
+    const T* row = proj + (long long)b * ld;
+    for (int d = tid; d < D; d += 128) {
+        qs[d] = ldf(row + q_off + hd * D + d) * qscale;
+        ks[d] = ldf(row + k_off + hd * D + d);
+    }
+    const float f = gf[(long long)b * H + hd], i = gi[(long long)b * H + hd];
+    const float m0 = fresh ? 0.f : state_m[(long long)line * H + hd];
+    const float mn = fmaxf(f + m0, i);
+    const float a = expf(f + m0 - mn), bw = expf(i - mn), e = expf(-mn);
+    __syncthreads();
+    const float vt = col_ok ? ldf(row + v_off + hd * Dv + col) * bw : 0.f;
+    float* Sg = state_s + ((long long)line * H + hd) * D * Dv + col;
+    float num = 0.f;
+#pragma unroll 8
+    for (int d = warp; d < D; d += 4) {
+        const float s_old = (fresh || !col_ok) ? 0.f : Sg[(long long)d * Dv];
+        const float sv = fmaf(a, s_old, ks[d] * vt);
+        if (col_ok) Sg[(long long)d * Dv] = sv;
+        num = fmaf(sv, qs[d], num);
+    }
+    const float* Ng = state_n + ((long long)line * H + hd) * D;
+    float nq = 0.f;
+    for (int d = tid; d < D; d += 128) {
+        const float nv = fmaf(a, fresh ? 0.f : Ng[d], bw * ks[d]);
+        nq = fmaf(nv, qs[d], nq);
+        if (blockIdx.x == 0) next_n[((long long)b * H + hd) * D + d] = nv;
+    }
+    nq = warp_sum(nq);
+    red[warp][lane] = num;
+    if (lane == 0) rednq[warp] = nq;
+    __syncthreads();
+    if (warp == 0 && col_ok) {
+        const float nsum = red[0][lane] + red[1][lane] + red[2][lane] + red[3][lane];
+        const float nqt = rednq[0] + rednq[1] + rednq[2] + rednq[3];
+        out[((long long)b * H + hd) * Dv + col] = nsum / (fmaxf(fabsf(nqt), e) + 1e-6f);
+    }
+    if (blockIdx.x == 0 && tid == 0) next_m[(long long)b * H + hd] = mn;
+}
+
 __global__ void mlstm_commit_kernel(const float* __restrict__ next_n, const float* __restrict__ next_m,
                                     float* __restrict__ state_n, float* __restrict__ state_m,
                                     const int* __restrict__ n_new, const int* __restrict__ seq_ids, int H, int D) {
@@ -265,6 +324,15 @@ int dispatch_scan(const void* proj, long long ld, int q_off, int k_off, int v_of
                   float* ss, float* sn, float* sm, float* nxn, float* nxm, float* out, const int* q_start,
                   const int* n_new, const int* seq_ids, int B, int Tn, int H, int D, int Dv, float qscale,
                   cudaStream_t st) {
+    if (Tn == 1 && n_new == nullptr) {                 // token generation
+        dim3 grid((Dv + 31) / 32, H, B);
+        mlstm_step_kernel<T><<<grid, 128, (size_t)2 * D * sizeof(float), st>>>(
+            (const T*)proj, ld, q_off, k_off, v_off, gi, gf, ss, sn, sm, nxn, nxm, out, q_start, seq_ids, H, D, Dv, qscale);
+        NXD_LAUNCH_CHECK();
+        mlstm_commit_kernel<<<dim3(H, B), 64, 0, st>>>(nxn, nxm, sn, sm, nullptr, seq_ids, H, D);
+        NXD_LAUNCH_CHECK();
+        return 0;
+    }
 #define NXD_SCAN_CASE(DPT)                                                                                             \
     if (D <= 4 * DPT)                                                                                                  \
         return launch_scan<T, DPT>(proj, ld, q_off, k_off, v_off, gi, gf, ss, sn, sm, nxn, nxm, out, q_start, n_new,   \

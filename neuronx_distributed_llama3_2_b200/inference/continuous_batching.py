@@ -44,6 +44,10 @@ class ContinuousBatcher:
         self.max_running = max_running or self.cache.lines
         self.sched = NativeScheduler(self.cache.pool, self.max_running)
         self.eos = eos_token_id if eos_token_id is not None else ic.eos_token_id
+        if pad_decode_to and getattr(self.cache, "states", None):
+            # a repeated row is harmless for keys and values (the same rows are written twice) but would apply a
+            # recurrent layer's state update twice
+            raise ValueError("pad_decode_to repeats a row of the batch: not usable with a model that keeps recurrent state")
         self.pad_decode_to = pad_decode_to
         self.buckets = sorted(context_buckets) if context_buckets else None
         self.pad_id = ic.pad_token_id

@@ -218,11 +218,12 @@ def test_attention_over_the_cache_chunks_and_sinks(dev, dt, paged, chunk, sink, 
 
 
 @case
-def test_wide_latent_rows_one_tensor_for_keys_and_values(dev, dt):
-    """One key/value head whose value is the first 256 columns of its 288-column key rows (the latent cache), twenty
-    query heads, a sink per head: token generation over a cache line and a prompt portion at an offset."""
+@pytest.mark.parametrize("D,Dv", [(288, 256), (576, 512), (40, 24)], ids=["288", "576", "40"])
+def test_wide_latent_rows_one_tensor_for_keys_and_values(dev, dt, D, Dv):
+    """One key/value head whose value is the first Dv columns of its D-column key rows (the latent cache), twenty query
+    heads, a sink per head: token generation over a cache line and a prompt portion at an offset."""
     torch.manual_seed(12)
-    H, D, Dv, S, n_ctx = 20, 288, 256, 160, 150
+    H, S, n_ctx = 20, 160, 150
     rows = (torch.randn(n_ctx, D) * 0.5).to(dt)
     cache = torch.zeros(2, 1, S, D, dtype=dt)
     cache[1, 0, :n_ctx] = rows
@@ -237,6 +238,28 @@ def test_wide_latent_rows_one_tensor_for_keys_and_values(dev, dt):
     part = wa.window_attention_prefill(q[None].to(dev), cache, cache[..., :Dv], torch.tensor([n_ctx - 9], device=dev), 0.1,
                                        seq_ids=line, sinks=sinks.to(dev))
     close(part[0], ref, dt)
+
+
+@case
+def test_expanded_latent_heads_of_192_and_128(dev, dt):
+    """Prompt attention over per-head expanded keys of 192 and values of 128 columns read through strided views (the
+    layout the latent mixer builds: [rows, positions, heads, columns]), with sinks and padding rows."""
+    torch.manual_seed(13)
+    B, T, H, D, Dv = 2, 70, 3, 192, 128
+    q = (torch.randn(B, T, H, D) * 0.3).to(dt)
+    keys = (torch.randn(B, T, H, D) * 0.3).to(dt)
+    vals = torch.randn(B, T, H, Dv).to(dt)
+    sinks = torch.tensor([0.0, 2.0, -1.0])
+    n_new = torch.tensor([70, 33])
+    out = wa.window_attention_prefill(q.to(dev), keys.to(dev).permute(0, 2, 1, 3), vals.to(dev).permute(0, 2, 1, 3),
+                                      torch.zeros(B, dtype=torch.int32, device=dev), 0.2, n_new=n_new.to(dev),
+                                      sinks=sinks.to(dev))
+    for b in range(B):
+        n = int(n_new[b])
+        ref = _attention_oracle(q[b, :n], keys[b, :n].transpose(0, 1), vals[b, :n].transpose(0, 1), torch.arange(n), 0.2,
+                                None, sinks)
+        close(out[b, :n], ref, dt)
+        assert float(out[b, n:].abs().sum()) == 0.0
 
 
 @case
@@ -322,6 +345,16 @@ def test_recurrent_gates_scan_and_state(dev, dt):
     close(torch.cat(got), ref, torch.float32, scale=5.0)
     for a, b in zip(st, st2):
         close(a[2], b[2].to("cpu", F64), torch.float32, scale=5.0)
+    # token generation: 40 tokens at once, then one token per call (no padding mask) on the same line
+    st5 = state(fill=2.0)
+    ml.mlstm_scan(proj[None, :40].to(dev).contiguous(), offs, gi[:40], gf[:40], st5, torch.tensor([0], device=dev), H, D,
+                  Dv, D ** -0.5, seq_ids=line)
+    steps = [ml.mlstm_scan(proj[None, t:t + 1].to(dev).contiguous(), offs, gi[t:t + 1], gf[t:t + 1], st5,
+                           torch.tensor([t], device=dev), H, D, Dv, D ** -0.5, seq_ids=line)[0, 0] for t in range(40, T)]
+    close(torch.stack(steps), ref[40:], torch.float32, scale=5.0)
+    for a, b in zip(st, st5):
+        close(a[2], b[2].to("cpu", F64), torch.float32, scale=5.0)
+    assert float((st5[0][1] - 2.0).abs().max()) == 0.0
     # the chunk-wise form: the whole prompt with chunks of 8 (five full chunks and a partial one), then two portions that
     # continue from the line's state, the second with padding behind it; same outputs, same final state
     st3 = state(fill=5.0)

@@ -32,6 +32,7 @@ from ..ops import latent_attention as la_ops
 from ..ops import mlstm as mlstm_ops
 from ..ops import rope as rope_ops
 from ..ops import window_attention as wa_ops
+from ..ops.linear import gemm_nt
 from .config import InferenceConfig
 from .kv_cache import KVCache
 from .model import KVCacheInferenceMixin
@@ -90,6 +91,15 @@ class RasodraInferenceModel(KVCacheInferenceMixin, RasodraForCausalLM):
         """Only the model's final norm comes through here: plain norm of the fp32 stream."""
         return norm(hidden, out_dtype=self.config.torch_dtype), None
 
+    @staticmethod
+    def _proj(linear, x: torch.Tensor) -> torch.Tensor:
+        """``x W^T (+ b)`` of a linear layer through the framework's GEMM dispatch directly (tensor-parallel size 1, no
+        gradients: the layer's autograd and collective wrappers would only cost host time per step)."""
+        y = gemm_nt(x.reshape(-1, x.shape[-1]), linear.weight)
+        if getattr(linear, "bias", None) is not None:
+            y = y.add_(linear.bias)
+        return y.reshape(x.shape[:-1] + (linear.weight.shape[0],))
+
     # -- mixers: h [B, T, W] in the activation dtype -> [B, T, W] ---------------------------------------------------------
     def _paged(self) -> dict:
         kc = self.kv_cache
@@ -107,7 +117,7 @@ class RasodraInferenceModel(KVCacheInferenceMixin, RasodraForCausalLM):
         B, T, _ = h.shape
         ck, cv = self.kv_cache.layer(i)
         paged = self._paged()
-        qk = mixer.qk_proj(h)
+        qk = self._proj(mixer.qk_proj, h)
         rope = self._rotary_tables(m.rot, h.device) if m.rot is not None else None
         q = wa_ops.qk_norm_cache_write(qk, ck, cv, q_start, m.heads, m.kv_heads, m.dim, m.vdim, cfg.rms_norm_eps,
                                        n_new=n_new, seq_ids=seq_ids, q_weight=mixer.q_norm, k_weight=mixer.k_norm,
@@ -128,7 +138,7 @@ class RasodraInferenceModel(KVCacheInferenceMixin, RasodraForCausalLM):
         else:
             o = wa_ops.window_attention_prefill(q, ck, cv, q_start, m.scale, n_new=n_new, seq_ids=seq_ids, chunk=m.chunk,
                                                 **paged)
-        return mixer.o_proj(o.reshape(B, T, m.heads * m.vdim))
+        return self._proj(mixer.o_proj, o.reshape(B, T, m.heads * m.vdim))
 
     def _latent_rows(self, ck, lines, n_ctx: int) -> torch.Tensor:
         """Rows ``[0, n_ctx)`` of the given cache lines of a latent cache tensor, ``[len(lines), n_ctx, rank + rot]``."""
@@ -154,7 +164,7 @@ class RasodraInferenceModel(KVCacheInferenceMixin, RasodraForCausalLM):
         N, H, R = B * T, m.heads, m.kv_rank
         ck, cv = self.kv_cache.layer(i)                    # cv: the first kv_rank columns of ck's rows
         paged = self._paged()
-        proj = mixer.in_proj(h)
+        proj = self._proj(mixer.in_proj, h)
         rope = self._rotary_tables(m.rot, h.device)
         if T == 1:
             # token generation: absorbed queries over the latent rows, value projection after the attention
@@ -172,7 +182,6 @@ class RasodraInferenceModel(KVCacheInferenceMixin, RasodraForCausalLM):
             q = la_ops.latent_prep(proj, 0, mixer.q_cols, None, ck, mixer.kv_norm, rope, q_start, H, m.dim, m.rot_dim, R,
                                    cfg.rms_norm_eps, n_new=n_new, seq_ids=seq_ids, **paged)
             n_ctx = self._step_context_len(q_start, n_new, T)
-            from ..ops.linear import gemm_nt
             lines = seq_ids if seq_ids is not None else torch.arange(B, device=h.device)
             rows = self._latent_rows(ck, lines, n_ctx)                               # [B, n_ctx, R + rot]
             c = rows[..., :R].reshape(B * n_ctx, R)
@@ -185,7 +194,7 @@ class RasodraInferenceModel(KVCacheInferenceMixin, RasodraForCausalLM):
                                                 sinks=mixer.sink).reshape(N, H, m.vdim)
         y = mlstm_ops.head_norm_gate(o, proj.reshape(N, -1), mixer.q_cols + mixer.kv_cols, H, m.vdim, None,
                                      cfg.rms_norm_eps, False, dt)
-        return mixer.o_proj(y.reshape(B, T, H * m.vdim))
+        return self._proj(mixer.o_proj, y.reshape(B, T, H * m.vdim))
 
     CHUNKWISE_MIN_TOKENS = 64
     CHUNKWISE_FP32 = False               # fp32 serving keeps the token-by-token scan (tests switch this on)
@@ -195,7 +204,7 @@ class RasodraInferenceModel(KVCacheInferenceMixin, RasodraForCausalLM):
         B, T, W = h.shape
         N, H = B * T, m.heads
         st = self.kv_cache.state(i)
-        proj = mixer.in_proj(h)
+        proj = self._proj(mixer.in_proj, h)
         gi, gf = mlstm_ops.mlstm_gates(h.reshape(N, W), mixer.gate_weight, mixer.gate_bias, H, m.gate_cap)
         # long bf16 steps take the chunk-wise form (matrix products); token generation, short steps and fp32 serving the
         # token-by-token scan
@@ -205,7 +214,7 @@ class RasodraInferenceModel(KVCacheInferenceMixin, RasodraForCausalLM):
                 m.dim ** -0.5, n_new=n_new, seq_ids=seq_ids)
         y = mlstm_ops.head_norm_gate(o.reshape(N, H, m.vdim), proj.reshape(N, -1), 2 * H * m.dim + H * m.vdim, H, m.vdim,
                                      mixer.out_norm, cfg.rms_norm_eps, True, dt)
-        return mixer.o_proj(y.reshape(B, T, H * m.vdim))
+        return self._proj(mixer.o_proj, y.reshape(B, T, H * m.vdim))
 
     _MIX = {"attention": _mix_attention, "latent_attention": _mix_latent, "mlstm": _mix_mlstm}
 
@@ -224,7 +233,7 @@ class RasodraInferenceModel(KVCacheInferenceMixin, RasodraForCausalLM):
             x, h = layer.norm1b.add_to(x, y, nxt, dt)
         else:
             x, h = layer.norm1b.add_to(x, y, layer.norm2, dt)
-            y = layer.mlp.down_proj(act_ops.relu_squared(layer.mlp.up_proj(h)))
+            y = self._proj(layer.mlp.down_proj, act_ops.relu_squared(self._proj(layer.mlp.up_proj, h)))
             x, h = layer.norm2b.add_to(x, y, nxt, dt)
         if self.layer_probe is not None:
             self.layer_probe(i, x)

@@ -171,6 +171,8 @@ def lib(group: Optional[str] = None) -> ctypes.CDLL:
     if _lib is not None:
         return _lib
     group = _preferred_group or group
+    if group is not None and group in _group_libs:       # already serving from the group's library: no file checks
+        return _group_libs[group]
     if group is not None and "NXD_B200_LIB" not in os.environ and _stale():
         with _lock:
             handle = _group_libs.get(group)

@@ -330,6 +330,13 @@ int nxd_latent_prep(int dtype, const void* proj, long long ld, int q_off, int kv
                     const int* block_table, int page_size, int table_cols, const float* c_weight, const float* rope_cos,
                     const float* rope_sin, const int* q_start, const int* n_new, const int* seq_ids, int B, int Tn, int H,
                     int dim, int rot, int rank, float eps, int max_pos, void* stream);
+/* bf16 token generation over latent rows (values = the first Dv columns of the D-column rows); partial: fp32 scratch
+ * [B, H, nsplit, Dv + 2]; returns 2 when no kernel is compiled for (D, Dv) */
+int nxd_latent_decode(const void* q, const void* cache, long long stride_line, long long row_pitch, const int* block_table,
+                      int page_size, int table_cols, void* out, float* partial, const int* positions, const int* seq_ids,
+                      const float* sinks, int B, int H, int D, int Dv, float scale, int nsplit, void* stream);
+int nxd_mlstm_chunk_states(float* u, const float* ftot, const float* mloc, const float* s0, const float* m0, float* s_out,
+                           float* m_start, float* m_out, long long BH, int NC, long long E, void* stream);
 /* recurrent matrix memory: fp32 gates (soft cap, log-sigmoid forget gate), scan over a step on the line's fp32 state,
  * gated / normalised head output, squared ReLU */
 int nxd_mlstm_gates(int dtype, const void* h, const void* w, const float* bias, float* gi, float* gf, long long N, int W,

@@ -84,3 +84,32 @@ def latent_prep(proj: torch.Tensor, q_off: int, kv_off: int, q_abs: Optional[tor
             else:
                 cache[line, 0, p] = rows[b, t]
     return ret
+
+
+TARGET_CTAS = 296          # two CTAs' worth of work per SM before the context is split further
+
+
+def latent_decode(q_abs: torch.Tensor, cache: torch.Tensor, value_cols: int, out: torch.Tensor, positions: torch.Tensor,
+                  seq_ids: Optional[torch.Tensor], sinks: Optional[torch.Tensor], scale: float,
+                  block_table: Optional[torch.Tensor], page_size: int) -> bool:
+    """Token generation over latent rows on tensor cores (``csrc/latent_attention.cu: latent_decode_kernel``):
+    ``q_abs [B, H, D]`` bf16 absorbed queries, ``cache [lines | pages, 1, rows, D]`` whose first ``value_cols`` columns
+    are the values, ``positions`` / ``seq_ids`` / ``block_table`` int32, ``sinks`` fp32.  Fills ``out [B, H, value_cols]``
+    and returns True; returns False when no kernel is compiled for these sizes (the caller takes the general kernels)."""
+    B, H, D = q_abs.shape
+    rows = block_table.shape[1] * page_size if block_table is not None else cache.shape[2]
+    ctas = ((H + 15) // 16) * B
+    nsplit = max(1, min(8, TARGET_CTAS // max(ctas, 1), (rows + 63) // 64))
+    partial = (torch.empty(B, H, nsplit, value_cols + 2, dtype=torch.float32, device=q_abs.device) if nsplit > 1 else None)
+    L = _lib.lib(GROUP)
+    rc = L.nxd_latent_decode(_lib.ptr(q_abs), _lib.ptr(cache), _c.c_longlong(cache.stride(0)),
+                             _c.c_longlong(cache.stride(2)), _lib.ptr(block_table),
+                             _c.c_int(page_size if block_table is not None else 0),
+                             _c.c_int(block_table.shape[1] if block_table is not None else 0), _lib.ptr(out),
+                             _lib.ptr(partial), _lib.ptr(positions), _lib.ptr(seq_ids), _lib.ptr(sinks), _c.c_int(B),
+                             _c.c_int(H), _c.c_int(D), _c.c_int(value_cols), _c.c_float(scale), _c.c_int(nsplit),
+                             _lib.stream_ptr())
+    if rc == 2:
+        return False
+    _lib.check(rc, "nxd_latent_decode", L)
+    return True

@@ -242,6 +242,15 @@ def window_attention_decode(q: torch.Tensor, cache_k: torch.Tensor, cache_v: tor
         pos, sid = _i32(positions), _i32(seq_ids)
         cargs, bt = _cache_args(cache_k, cache_v, block_table, page_size, rows=True)
         sk = sinks.float().contiguous() if sinks is not None else None
+        if (impl == "auto" and q.dtype == torch.bfloat16 and G == 1 and not w and not chunk and slopes is None
+                and cache_v.data_ptr() == cache_k.data_ptr() and cache_v.stride(2) == cache_k.stride(2)
+                and cache_v.stride(0) == cache_k.stride(0)):
+            # latent rows (one key/value head, values = the first columns of the key rows): the kernel that streams the
+            # rows once per 16 query heads, with the context split over CTAs when the batch alone does not fill the GPU
+            from . import latent_attention as la
+
+            if la.latent_decode(q, cache_k, Dv, out, pos, sid, sk, scale, bt, page_size):
+                return out
         L = _lib.lib(GROUP)
         rc = L.nxd_masked_attn_decode(_c.c_int(_code(q.dtype)), _lib.ptr(q), _lib.ptr(cache_k), _lib.ptr(cache_v), *cargs,
                                       _lib.ptr(out), _lib.ptr(pos), _lib.ptr(sid), _lib.ptr(slopes), _lib.ptr(sk),

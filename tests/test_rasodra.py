@@ -238,6 +238,30 @@ def test_wide_latent_rows_one_tensor_for_keys_and_values(dev, dt, D, Dv):
     part = wa.window_attention_prefill(q[None].to(dev), cache, cache[..., :Dv], torch.tensor([n_ctx - 9], device=dev), 0.1,
                                        seq_ids=line, sinks=sinks.to(dev))
     close(part[0], ref, dt)
+    # three rows of different lengths on a paged cache, with the context split over CTAs and in one piece
+    page, lens, lines3 = 16, [150, 70, 5], [1, 0, 2]
+    g = torch.Generator().manual_seed(3)
+    table = torch.randperm(30, generator=g).to(torch.int32).reshape(3, 10)
+    paged = torch.zeros(30, 1, page, D, dtype=dt)
+    seqs = [(torch.randn(n, D, generator=g) * 0.5).to(dt) for n in lens]
+    for ln, rows_ in zip(lines3, seqs):
+        for pos in range(rows_.shape[0]):
+            paged[table[ln, pos // page], 0, pos % page] = rows_[pos]
+    paged = paged.to(dev)
+    q3 = (torch.randn(3, H, D, generator=g) * 0.5).to(dt)
+    want = torch.stack([_attention_oracle(q3[i:i + 1], seqs[i][None], seqs[i][None, :, :Dv], torch.tensor([lens[i] - 1]), 0.1,
+                                          None, sinks)[0] for i in range(3)])
+    from neuronx_distributed_llama3_2_b200.ops import latent_attention as la_mod
+
+    for target in (la_mod.TARGET_CTAS, 1):
+        old, la_mod.TARGET_CTAS = la_mod.TARGET_CTAS, target
+        try:
+            got = wa.window_attention_decode(q3.to(dev), paged, paged[..., :Dv], torch.tensor([n - 1 for n in lens], device=dev),
+                                             0.1, seq_ids=torch.tensor(lines3, dtype=torch.int32, device=dev),
+                                             sinks=sinks.to(dev), block_table=table.to(dev), page_size=page)
+        finally:
+            la_mod.TARGET_CTAS = old
+        close(got, want, dt)
 
 
 @case
